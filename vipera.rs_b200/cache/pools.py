@@ -32,22 +32,30 @@ class CacheGroup:
     num_kv_heads: int
     head_dim: int
     window: Optional[int]
+    value_dim: int = 0       # 0: values are as long as keys
+    keep_first: int = 0
     slots: List[int] = field(default_factory=list)  # cache slots (of the schedule) in this group
 
+    @property
+    def v_dim(self) -> int:
+        return self.value_dim or self.head_dim
+
     def bytes_per_token(self, element_bytes: int) -> int:
-        return 2 * len(self.slots) * self.num_kv_heads * self.head_dim * element_bytes
+        return len(self.slots) * self.num_kv_heads * (self.head_dim + self.v_dim) * element_bytes
 
 
 def plan_groups(cache_requests: Dict[int, object]) -> Tuple[List[CacheGroup], Dict[int, FixedState]]:
     """Sort the cache slots of a model into paged groups and fixed-state slots."""
-    groups: Dict[Tuple[int, int, Optional[int]], CacheGroup] = {}
+    groups: Dict[tuple, CacheGroup] = {}
     states: Dict[int, FixedState] = {}
     for slot in sorted(cache_requests):
         request = cache_requests[slot]
         if request is None:
             continue
         if isinstance(request, PagedKV):
-            key = (request.num_kv_heads, request.head_dim, request.window)
+            value_dim = request.value_dim if request.value_dim and request.value_dim != request.head_dim else 0
+            keep_first = int(request.keep_first or 0) if request.window else 0
+            key = (request.num_kv_heads, request.head_dim, request.window, value_dim, keep_first)
             if key not in groups:
                 groups[key] = CacheGroup(*key)
             groups[key].slots.append(slot)
@@ -74,7 +82,8 @@ class CachePools:
         self.num_pages = [int(n) for n in num_pages]
         runtime = runtime_module()
         self.manager = runtime.CacheManager(
-            [(self.page_size, pages, group.window or 0) for group, pages in zip(self.groups, self.num_pages)],
+            [(self.page_size, pages, group.window or 0, group.keep_first)
+             for group, pages in zip(self.groups, self.num_pages)],
             int(num_state_slots),
             # pages of a prompt prefix can be shared only where the pages are all a request keeps:
             # a mixer with a state of its own would have to store that state at every page's end
@@ -89,20 +98,23 @@ class CachePools:
         # that went past either end of a pool.
         self._guards: List[torch.Tensor] = []
         for index, (group, pages) in enumerate(zip(self.groups, self.num_pages)):
-            shape = (len(group.slots), 2, pages + 1, self.page_size, group.num_kv_heads, group.head_dim)
-            count = 1
-            for extent in shape:
-                count *= extent
-            guard = self.page_size * group.num_kv_heads * group.head_dim
+            rows = (pages + 1) * self.page_size * group.num_kv_heads     # key (or value) rows of one slot
+            count = len(group.slots) * rows * (group.head_dim + group.v_dim)
+            guard = self.page_size * group.num_kv_heads * max(group.head_dim, group.v_dim)
             storage = torch.zeros(count + 2 * guard, dtype=dtype, device=device)
             storage[:guard].view(torch.int16 if storage.element_size() == 2 else torch.int32).fill_(GUARD_WORD)
             storage[guard + count:].view(torch.int16 if storage.element_size() == 2 else torch.int32).fill_(GUARD_WORD)
             self._guards.extend([storage[:guard], storage[guard + count:]])
-            pool = storage[guard:guard + count].view(shape)
+            pool = storage[guard:guard + count]
             self.pool_tensors.append(pool)
+            page_shape = (pages + 1, self.page_size, group.num_kv_heads)
             for position, slot in enumerate(group.slots):
-                self.views[slot] = PagedKVView(index, pool[position, 0], pool[position, 1], self.page_size,
-                                               group.window)
+                # a slot's keys, then its values: [slot][k | v][page][position][kv head][d or value size]
+                base = position * rows * (group.head_dim + group.v_dim)
+                k = pool[base:base + rows * group.head_dim].view(*page_shape, group.head_dim)
+                v = pool[base + rows * group.head_dim:base + rows * (group.head_dim + group.v_dim)].view(
+                    *page_shape, group.v_dim)
+                self.views[slot] = PagedKVView(index, k, v, self.page_size, group.window, group.keep_first)
         for slot, request in self.states.items():
             data = torch.zeros((int(num_state_slots), *request.shape), dtype=request.dtype, device=device)
             self.views[slot] = StateView(data)

@@ -19,6 +19,7 @@ from .registry import (
 )
 from .spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 from .qwen2 import Qwen2Config, qwen2_model_spec
+from .nobupel import NobupelConfig, nobupel_model_spec
 
 
 def read_config_json(model_dir: str) -> Dict[str, Any]:
@@ -38,11 +39,14 @@ def read_config_json(model_dir: str) -> Dict[str, Any]:
 
 
 def architecture_of(data: Dict[str, Any]) -> Architecture:
-    """The registered architecture config.json names in ``architectures[0]``."""
+    """The registered architecture config.json names in ``architectures[0]`` (or, in files that
+    name one only, in ``architecture``)."""
     names = data.get("architectures")
+    if not names and isinstance(data.get("architecture"), str):
+        names = [data["architecture"]]
     if not names or not isinstance(names, list):
         raise UnsupportedError(
-            "config.json has no 'architectures' list; registered: "
+            "config.json has no 'architectures' list and no 'architecture'; registered: "
             + ", ".join(ARCHITECTURES.names())
         )
     return ARCHITECTURES.find(str(names[0]))
@@ -59,6 +63,6 @@ __all__ = [
     "ARCHITECTURES", "BLOCKS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITION_ENCODINGS",
     "Architecture", "Registry", "register_architecture",
     "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry",
-    "Qwen2Config", "qwen2_model_spec",
+    "Qwen2Config", "qwen2_model_spec", "NobupelConfig", "nobupel_model_spec",
     "read_config_json", "architecture_of", "load_config",
 ]

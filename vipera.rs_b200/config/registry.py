@@ -63,6 +63,9 @@ class Architecture:
     # Other names a weight file may use: ``tensor_alias(name_in_file)`` returns the name the
     # parts ask for, or None where the name is not an alias.
     tensor_alias: Optional[Callable[[str], Optional[str]]] = None
+    # The inverse where the architecture's own files use other names than the parts:
+    # ``stored_name(name_a_part_asks_for)`` is the name a written weight file stores it under.
+    stored_name: Optional[Callable[[str], str]] = None
 
 
 ARCHITECTURES: Registry[Architecture] = Registry("architecture")
@@ -73,7 +76,8 @@ POSITION_ENCODINGS: Registry[type] = Registry("position encoding")
 BLOCKS: Registry[type] = Registry("block arrangement")
 
 
-def register_architecture(name, config_from_dict, model_spec, *, tensor_alias=None, replace=False) -> Architecture:
+def register_architecture(name, config_from_dict, model_spec, *, tensor_alias=None, stored_name=None,
+                          replace=False) -> Architecture:
     return ARCHITECTURES.register(
-        name, Architecture(name, config_from_dict, model_spec, tensor_alias), replace=replace
+        name, Architecture(name, config_from_dict, model_spec, tensor_alias, stored_name), replace=replace
     )

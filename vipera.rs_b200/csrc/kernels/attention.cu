@@ -10,8 +10,13 @@
 // Keys are found through the block table: position j lives in page table[j / page], slot
 // j % page (model.rs:1507-1542).
 //
+// Three options beyond that definition, each a parameter: values of another size than keys
+// (`value_dim`); with a window, the first `keep_first` keys of a request stay visible to every
+// later query, at their true positions; and a sink, an extra key of score 0 without a value,
+// which adds exp(0 - max) to the softmax's denominator (p_j = e^{s_j} / (1 + sum e^{s_j})).
+//
 // This kernel is the attention of the 32-bit path and takes every head size that is a
-// multiple of 16 up to 256, any number of heads and groups, any page size.
+// multiple of 8 up to 256 (keys and values each), any number of heads and groups, any page size.
 #include "common.cuh"
 
 constexpr int kWarpsPerBlock = 4;
@@ -56,7 +61,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 attention_kernel(const T* __restrict__ q, T* __restrict__ out, const T* __restrict__ k_pool,
                  const T* __restrict__ v_pool, const int* __restrict__ token_seq,
                  const int* __restrict__ positions, const int* __restrict__ block_table, int table_width,
-                 int page_size, int num_heads, int num_kv_heads, int head_dim, float scale, int window) {
+                 int page_size, int num_heads, int num_kv_heads, int head_dim, int value_dim, float scale,
+                 int window, int keep_first, int sink) {
   __shared__ float q_shared[kWarpsPerBlock][kMaxHeadDim];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
@@ -78,10 +84,16 @@ attention_kernel(const T* __restrict__ q, T* __restrict__ out, const T* __restri
   for (int i = 0; i < kMaxHeadDim / 32; ++i) acc[i] = 0.0f;
   float running_max = -INFINITY, running_sum = 0.0f;
   const size_t row_stride = static_cast<size_t>(num_kv_heads) * head_dim;
+  const size_t v_stride = static_cast<size_t>(num_kv_heads) * value_dim;
+  // two runs of keys: the kept first ones that the window has left behind, then the window
+  const int kept_end = window > 0 ? min(keep_first, first) : 0;
 
-  for (int base = first; base <= position; base += 32) {
+  for (int run = 0; run < 2; ++run) {
+  const int run_first = run == 0 ? 0 : first;
+  const int run_last = run == 0 ? kept_end - 1 : position;
+  for (int base = run_first; base <= run_last; base += 32) {
     const int j = base + lane;
-    const bool valid = j <= position;
+    const bool valid = j <= run_last;
     float score = -INFINITY;
     if (valid) {
       const int page = table[j / page_size];
@@ -96,39 +108,52 @@ attention_kernel(const T* __restrict__ q, T* __restrict__ out, const T* __restri
     running_max = new_max;
 #pragma unroll
     for (int i = 0; i < kMaxHeadDim / 32; ++i) acc[i] *= alpha;
-    const int count = min(32, position - base + 1);
+    const int count = min(32, run_last - base + 1);
     for (int jj = 0; jj < count; ++jj) {
       const float w = __shfl_sync(0xffffffffu, weight, jj);
       const int key = base + jj;
       const int page = table[key / page_size];
-      const T* v_row = v_pool + (static_cast<size_t>(page) * page_size + key % page_size) * row_stride +
-                       static_cast<size_t>(kv_head) * head_dim;
+      const T* v_row = v_pool + (static_cast<size_t>(page) * page_size + key % page_size) * v_stride +
+                       static_cast<size_t>(kv_head) * value_dim;
 #pragma unroll
       for (int i = 0; i < kMaxHeadDim / 32; ++i) {
         const int e = lane + 32 * i;
-        if (e < head_dim) acc[i] = fmaf(w, to_float<T>(v_row[e]), acc[i]);
+        if (e < value_dim) acc[i] = fmaf(w, to_float<T>(v_row[e]), acc[i]);
       }
     }
   }
+  }
+  if (sink) {
+    // the sink's score is 0: fold it in like one more key whose value is zero
+    const float new_max = fmaxf(running_max, 0.0f);
+    const float alpha = expf(running_max - new_max);
+    running_sum = running_sum * alpha + expf(0.0f - new_max);
+#pragma unroll
+    for (int i = 0; i < kMaxHeadDim / 32; ++i) acc[i] *= alpha;
+  }
   const float inverse = 1.0f / running_sum;
-  T* out_row = out + (static_cast<size_t>(t) * num_heads + h) * head_dim;
+  T* out_row = out + (static_cast<size_t>(t) * num_heads + h) * value_dim;
 #pragma unroll
   for (int i = 0; i < kMaxHeadDim / 32; ++i) {
     const int e = lane + 32 * i;
-    if (e < head_dim) out_row[e] = from_float<T>(acc[i] * inverse);
+    if (e < value_dim) out_row[e] = from_float<T>(acc[i] * inverse);
   }
 }
 
-// q and out are [tokens, heads, d]; the pools are [pages, page_size, kv_heads, d].
+// q is [tokens, heads, d] and out [tokens, heads, value_dim]; the key pool is
+// [pages, page_size, kv_heads, d] and the value pool the same with value_dim last.
 // token_seq[t] is the row of block_table (width table_width) of token t's request and
 // positions[t] its position.  The keys and values of this step's tokens must already be
-// in the cache.  window = 0 means every earlier key is visible.
+// in the cache.  window = 0 means every earlier key is visible; keep_first counts only with a
+// window; sink != 0 adds the sink to the denominator.
 VIPERA_API int vipera_attention(const void* q, void* out, int dtype, const void* k_pool, const void* v_pool,
                                 const int* token_seq, const int* positions, const int* block_table,
                                 int table_width, int page_size, int num_tokens, int num_heads,
-                                int num_kv_heads, int head_dim, float scale, int window, void* stream) {
+                                int num_kv_heads, int head_dim, int value_dim, float scale, int window,
+                                int keep_first, int sink, void* stream) {
   if (num_tokens <= 0) return VIPERA_OK;
-  if (head_dim <= 0 || head_dim % 16 != 0 || head_dim > kMaxHeadDim) return VIPERA_BAD_SHAPE;
+  if (head_dim <= 0 || head_dim % 8 != 0 || head_dim > kMaxHeadDim) return VIPERA_BAD_SHAPE;
+  if (value_dim <= 0 || value_dim % 8 != 0 || value_dim > kMaxHeadDim || keep_first < 0) return VIPERA_BAD_SHAPE;
   if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads != 0) return VIPERA_BAD_SHAPE;
   if (page_size <= 0 || table_width <= 0 || window < 0) return VIPERA_BAD_ARGUMENT;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -137,12 +162,13 @@ VIPERA_API int vipera_attention(const void* q, void* out, int dtype, const void*
     attention_kernel<float><<<grid, kWarpsPerBlock * 32, 0, s>>>(
         static_cast<const float*>(q), static_cast<float*>(out), static_cast<const float*>(k_pool),
         static_cast<const float*>(v_pool), token_seq, positions, block_table, table_width, page_size,
-        num_heads, num_kv_heads, head_dim, scale, window);
+        num_heads, num_kv_heads, head_dim, value_dim, scale, window, keep_first, sink);
   else if (dtype == VIPERA_BF16)
     attention_kernel<__nv_bfloat16><<<grid, kWarpsPerBlock * 32, 0, s>>>(
         static_cast<const __nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(out),
         static_cast<const __nv_bfloat16*>(k_pool), static_cast<const __nv_bfloat16*>(v_pool), token_seq,
-        positions, block_table, table_width, page_size, num_heads, num_kv_heads, head_dim, scale, window);
+        positions, block_table, table_width, page_size, num_heads, num_kv_heads, head_dim, value_dim, scale, window,
+        keep_first, sink);
   else
     return VIPERA_BAD_DTYPE;
   return vipera_launch_status();

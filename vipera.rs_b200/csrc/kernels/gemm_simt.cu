@@ -9,10 +9,12 @@
 //
 // Epilogues:
 //   STORE     out[m, n] = acc (+ bias[n]), stored as float or bfloat16
-//   RESIDUAL  resid[m, n] += acc            (32-bit residual stream)
-//   SWIGLU    W holds gate and up rows interleaved in groups of 16 (16 gate rows, then the
-//             16 up rows of the same features); out[m, f] = up * silu(gate), silu(z) = z/(1+exp(-z))
-//             (model.rs:4368-4374)
+//   RESIDUAL  resid[m, n] += acc (+ bias[n])  (32-bit residual stream)
+//   SWIGLU    (a gated unit) W holds gate and up rows interleaved in groups of 16 (16 gate rows,
+//             then the 16 up rows of the same features, and the bias likewise);
+//             out[m, f] = (up + bias) * act(gate + bias), act = silu, silu(z) = z/(1+exp(-z))
+//             (model.rs:4368-4374), or the tanh form of gelu,
+//             0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
 #include "common.cuh"
 
 enum GemmEpilogue { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2 };
@@ -22,7 +24,7 @@ constexpr int BM = 64, BN = 64, BK = 16, PAD = 4;
 template <typename TA, typename TW, typename TO, int EPI>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, int M, int N, int K,
-                 const float* __restrict__ bias, TO* __restrict__ out, float* __restrict__ resid) {
+                 const float* __restrict__ bias, TO* __restrict__ out, float* __restrict__ resid, int activation) {
   __shared__ float As[BK][BM + PAD];
   __shared__ float Ws[BK][BN + PAD];
   const int tid = threadIdx.x;
@@ -76,8 +78,12 @@ gemm_simt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, int M, int 
         const int n_gate = n0 + tx + 32 * pair;
         if (n_gate + 16 >= N) continue;
         const int feature = n0 / 2 + 16 * pair + tx;
-        const float gate = acc[i][2 * pair], up = acc[i][2 * pair + 1];
-        const float value = up * (gate / (1.0f + expf(-gate)));
+        float gate = acc[i][2 * pair], up = acc[i][2 * pair + 1];
+        if (bias) {
+          gate += bias[n_gate];
+          up += bias[n_gate + 16];
+        }
+        const float value = up * gate_activation(gate, activation);
         out[static_cast<size_t>(m) * (N / 2) + feature] = from_float<TO>(value);
       }
     } else {
@@ -90,6 +96,7 @@ gemm_simt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, int M, int 
           if (bias) value += bias[n];
           out[static_cast<size_t>(m) * N + n] = from_float<TO>(value);
         } else {
+          if (bias) value += bias[n];
           resid[static_cast<size_t>(m) * N + n] += value;
         }
       }
@@ -99,26 +106,26 @@ gemm_simt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, int M, int 
 
 template <typename TA, typename TW>
 static int launch_typed(const TA* A, const TW* W, int M, int N, int K, int epilogue, const float* bias,
-                        void* out, int out_dtype, float* resid, cudaStream_t s) {
+                        void* out, int out_dtype, float* resid, int activation, cudaStream_t s) {
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   if (epilogue == EPI_RESIDUAL) {
     if (!resid) return VIPERA_BAD_ARGUMENT;
-    gemm_simt_kernel<TA, TW, float, EPI_RESIDUAL><<<grid, 256, 0, s>>>(A, W, M, N, K, nullptr, nullptr, resid);
+    gemm_simt_kernel<TA, TW, float, EPI_RESIDUAL><<<grid, 256, 0, s>>>(A, W, M, N, K, bias, nullptr, resid, activation);
   } else if (epilogue == EPI_STORE) {
     if (!out) return VIPERA_BAD_ARGUMENT;
     if (out_dtype == VIPERA_F32)
-      gemm_simt_kernel<TA, TW, float, EPI_STORE><<<grid, 256, 0, s>>>(A, W, M, N, K, bias, static_cast<float*>(out), nullptr);
+      gemm_simt_kernel<TA, TW, float, EPI_STORE><<<grid, 256, 0, s>>>(A, W, M, N, K, bias, static_cast<float*>(out), nullptr, activation);
     else if (out_dtype == VIPERA_BF16)
-      gemm_simt_kernel<TA, TW, __nv_bfloat16, EPI_STORE><<<grid, 256, 0, s>>>(A, W, M, N, K, bias, static_cast<__nv_bfloat16*>(out), nullptr);
+      gemm_simt_kernel<TA, TW, __nv_bfloat16, EPI_STORE><<<grid, 256, 0, s>>>(A, W, M, N, K, bias, static_cast<__nv_bfloat16*>(out), nullptr, activation);
     else
       return VIPERA_BAD_DTYPE;
   } else if (epilogue == EPI_SWIGLU) {
     if (!out) return VIPERA_BAD_ARGUMENT;
     if (N % 32 != 0) return VIPERA_BAD_SHAPE;  // gate/up groups of 16 must pair up
     if (out_dtype == VIPERA_F32)
-      gemm_simt_kernel<TA, TW, float, EPI_SWIGLU><<<grid, 256, 0, s>>>(A, W, M, N, K, nullptr, static_cast<float*>(out), nullptr);
+      gemm_simt_kernel<TA, TW, float, EPI_SWIGLU><<<grid, 256, 0, s>>>(A, W, M, N, K, bias, static_cast<float*>(out), nullptr, activation);
     else if (out_dtype == VIPERA_BF16)
-      gemm_simt_kernel<TA, TW, __nv_bfloat16, EPI_SWIGLU><<<grid, 256, 0, s>>>(A, W, M, N, K, nullptr, static_cast<__nv_bfloat16*>(out), nullptr);
+      gemm_simt_kernel<TA, TW, __nv_bfloat16, EPI_SWIGLU><<<grid, 256, 0, s>>>(A, W, M, N, K, bias, static_cast<__nv_bfloat16*>(out), nullptr, activation);
     else
       return VIPERA_BAD_DTYPE;
   } else {
@@ -129,19 +136,34 @@ static int launch_typed(const TA* A, const TW* W, int M, int N, int K, int epilo
 
 // A is [M, K] and W is [N, K], both row-major and contiguous.  For SWIGLU, N counts the
 // interleaved gate and up rows (twice the intermediate size) and out is [M, N/2].
-VIPERA_API int vipera_gemm_simt(const void* A, int a_dtype, const void* W, int w_dtype, int M, int N, int K,
-                                int epilogue, const float* bias, void* out, int out_dtype, float* resid,
-                                void* stream) {
+static int run_simt(const void* A, int a_dtype, const void* W, int w_dtype, int M, int N, int K, int epilogue,
+                    const float* bias, void* out, int out_dtype, float* resid, int activation, void* stream) {
   if (M <= 0) return VIPERA_OK;
   if (N <= 0 || K <= 0) return VIPERA_BAD_SHAPE;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (a_dtype == VIPERA_F32 && w_dtype == VIPERA_F32)
-    return launch_typed(static_cast<const float*>(A), static_cast<const float*>(W), M, N, K, epilogue, bias, out, out_dtype, resid, s);
+    return launch_typed(static_cast<const float*>(A), static_cast<const float*>(W), M, N, K, epilogue, bias, out, out_dtype, resid, activation, s);
   if (a_dtype == VIPERA_BF16 && w_dtype == VIPERA_BF16)
-    return launch_typed(static_cast<const __nv_bfloat16*>(A), static_cast<const __nv_bfloat16*>(W), M, N, K, epilogue, bias, out, out_dtype, resid, s);
+    return launch_typed(static_cast<const __nv_bfloat16*>(A), static_cast<const __nv_bfloat16*>(W), M, N, K, epilogue, bias, out, out_dtype, resid, activation, s);
   if (a_dtype == VIPERA_F32 && w_dtype == VIPERA_BF16)
-    return launch_typed(static_cast<const float*>(A), static_cast<const __nv_bfloat16*>(W), M, N, K, epilogue, bias, out, out_dtype, resid, s);
+    return launch_typed(static_cast<const float*>(A), static_cast<const __nv_bfloat16*>(W), M, N, K, epilogue, bias, out, out_dtype, resid, activation, s);
   return VIPERA_BAD_DTYPE;
+}
+
+VIPERA_API int vipera_gemm_simt(const void* A, int a_dtype, const void* W, int w_dtype, int M, int N, int K,
+                                int epilogue, const float* bias, void* out, int out_dtype, float* resid,
+                                void* stream) {
+  // the form the earlier callers know: bias with STORE only, silu in the gated unit
+  return run_simt(A, a_dtype, W, w_dtype, M, N, K, epilogue, epilogue == EPI_STORE ? bias : nullptr, out, out_dtype,
+                  resid, ACT_SILU, stream);
+}
+
+// The same with a bias in every ending and the gated unit's activation chosen (ACT_SILU, ACT_GELU_TANH).
+VIPERA_API int vipera_gemm_simt_act(const void* A, int a_dtype, const void* W, int w_dtype, int M, int N, int K,
+                                    int epilogue, const float* bias, void* out, int out_dtype, float* resid,
+                                    int activation, void* stream) {
+  if (activation != ACT_SILU && activation != ACT_GELU_TANH) return VIPERA_BAD_ARGUMENT;
+  return run_simt(A, a_dtype, W, w_dtype, M, N, K, epilogue, bias, out, out_dtype, resid, activation, stream);
 }
 
 VIPERA_API const char* vipera_gemm_simt_status_text(int status) { return vipera_status_text(status); }

@@ -98,6 +98,86 @@ rope_cache_kernel(const float* __restrict__ qkv, T* __restrict__ q_out, int num_
   }
 }
 
+// The general form: only the first `rot_dims` values of a q or k head turn (value i with value
+// i + rot_dims/2 in the NeoX pairing, 2i with 2i + 1 in the interleaved one; the tables are
+// [positions, rot_dims/2]), the rest pass unchanged, and a value row has `value_dim` values.
+// Input [tokens, heads*d + kv_heads*d + kv_heads*value_dim].  One block per token, a thread per value.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rope_cache_partial_kernel(const float* __restrict__ qkv, T* __restrict__ q_out, int num_heads, int num_kv_heads,
+                          int head_dim, int value_dim, int rot_dims, const int* __restrict__ positions,
+                          const float* __restrict__ cos_table, const float* __restrict__ sin_table, int style,
+                          T* __restrict__ k_pool, T* __restrict__ v_pool, const int* __restrict__ token_seq,
+                          const int* __restrict__ block_table, int table_width, int page_size, int write_cache) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int qk_width = (num_heads + num_kv_heads) * head_dim;
+  const int v_width = num_kv_heads * value_dim;
+  const float* row = qkv + static_cast<size_t>(t) * (qk_width + v_width);
+  const int position = positions[t];
+  T* k_row = nullptr;
+  T* v_row = nullptr;
+  if (write_cache) {
+    const int page = block_table[static_cast<size_t>(token_seq[t]) * table_width + position / page_size];
+    if (page >= 0) {
+      const size_t at = static_cast<size_t>(page) * page_size + position % page_size;
+      k_row = k_pool + at * num_kv_heads * head_dim;
+      v_row = v_pool + at * num_kv_heads * value_dim;
+    }
+  }
+  const int half = rot_dims >> 1;
+  const float* cos_row = cos_table ? cos_table + static_cast<size_t>(position) * half : nullptr;
+  const float* sin_row = sin_table ? sin_table + static_cast<size_t>(position) * half : nullptr;
+  for (int item = threadIdx.x; item < qk_width; item += blockDim.x) {
+    const int h = item / head_dim, e = item % head_dim;
+    const float* head = row + static_cast<size_t>(h) * head_dim;
+    float value = head[e];
+    if (style != ROPE_NONE && e < rot_dims) {
+      if (style == ROPE_INTERLEAVED) {
+        const int i = e >> 1;
+        const float a = head[2 * i], b = head[2 * i + 1], c = cos_row[i], s = sin_row[i];
+        value = (e & 1) ? a * s + b * c : a * c - b * s;
+      } else {
+        const int i = e < half ? e : e - half;
+        const float a = head[i], b = head[i + half], c = cos_row[i], s = sin_row[i];
+        value = e < half ? a * c - b * s : a * s + b * c;
+      }
+    }
+    if (h < num_heads) q_out[(static_cast<size_t>(t) * num_heads + h) * head_dim + e] = from_float<T>(value);
+    else if (k_row) k_row[static_cast<size_t>(h - num_heads) * head_dim + e] = from_float<T>(value);
+  }
+  if (v_row)
+    for (int item = threadIdx.x; item < v_width; item += blockDim.x) v_row[item] = from_float<T>(row[qk_width + item]);
+}
+
+VIPERA_API int vipera_rope_cache_partial(const float* qkv, void* q_out, int dtype, int num_tokens, int num_heads,
+                                         int num_kv_heads, int head_dim, int value_dim, int rot_dims,
+                                         const int* positions, const float* cos_table, const float* sin_table,
+                                         int style, void* k_pool, void* v_pool, const int* token_seq,
+                                         const int* block_table, int table_width, int page_size, int write_cache,
+                                         void* stream) {
+  if (num_tokens <= 0) return VIPERA_OK;
+  if (head_dim <= 0 || value_dim <= 0 || num_heads <= 0 || num_kv_heads <= 0) return VIPERA_BAD_SHAPE;
+  if (rot_dims < 0 || (rot_dims & 1) || rot_dims > head_dim) return VIPERA_BAD_SHAPE;
+  if (style != ROPE_NONE && rot_dims > 0 && (!cos_table || !sin_table)) return VIPERA_BAD_ARGUMENT;
+  if (write_cache && (!k_pool || !v_pool || !token_seq || !block_table || page_size <= 0)) return VIPERA_BAD_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  dim3 grid(num_tokens);
+  const int work = (num_heads + num_kv_heads) * head_dim;
+  const int threads = work >= 256 ? 256 : (work >= 128 ? 128 : 64);
+  if (dtype == VIPERA_F32)
+    return vipera_launch(rope_cache_partial_kernel<float>, grid, threads, 0, s, qkv, static_cast<float*>(q_out), num_heads,
+        num_kv_heads, head_dim, value_dim, rot_dims, positions, cos_table, sin_table, style, static_cast<float*>(k_pool),
+        static_cast<float*>(v_pool), token_seq, block_table, table_width, page_size, write_cache);
+  if (dtype == VIPERA_BF16)
+    return vipera_launch(rope_cache_partial_kernel<__nv_bfloat16>, grid, threads, 0, s, qkv, static_cast<__nv_bfloat16*>(q_out),
+        num_heads, num_kv_heads, head_dim, value_dim, rot_dims, positions, cos_table, sin_table, style,
+        static_cast<__nv_bfloat16*>(k_pool), static_cast<__nv_bfloat16*>(v_pool), token_seq, block_table, table_width,
+        page_size, write_cache);
+  return VIPERA_BAD_DTYPE;
+}
+
 VIPERA_API int vipera_rope_cache(const float* qkv, void* q_out, int dtype, int num_tokens, int num_heads,
                                  int num_kv_heads, int head_dim, const int* positions,
                                  const float* cos_table, const float* sin_table, int style, void* k_pool,

@@ -101,13 +101,16 @@ PYBIND11_MODULE(_vipera_runtime, m) {
 
   // ---- cache manager ---------------------------------------------------------------
   py::class_<CacheManager>(m, "CacheManager")
-      .def(py::init([](const std::vector<std::tuple<int, int, int>>& groups, int slots, bool reuse) {
+      .def(py::init([](const std::vector<py::tuple>& groups, int slots, bool reuse) {
+             // a group is (page size, pages, window) or (page size, pages, window, kept first tokens)
              std::vector<GroupConfig> configs;
-             for (const auto& g : groups) {
+             for (const py::tuple& g : groups) {
+               if (g.size() != 3 && g.size() != 4) throw InvalidArgument("a group is (page_size, num_pages, window[, keep_first])");
                GroupConfig c;
-               c.page_size = std::get<0>(g);
-               c.num_pages = std::get<1>(g);
-               c.window = std::get<2>(g);
+               c.page_size = g[0].cast<int>();
+               c.num_pages = g[1].cast<int>();
+               c.window = g[2].cast<int>();
+               if (g.size() == 4) c.keep_first = g[3].cast<int>();
                configs.push_back(c);
              }
              return new CacheManager(configs, slots, reuse);
@@ -126,7 +129,7 @@ PYBIND11_MODULE(_vipera_runtime, m) {
       .def_property_readonly("free_state_slots", &CacheManager::free_state_slots)
       .def("group", [](const CacheManager& c, int g) {
         const GroupConfig& config = c.group(g);
-        return py::make_tuple(config.page_size, config.num_pages, config.window);
+        return py::make_tuple(config.page_size, config.num_pages, config.window, config.keep_first);
       })
       .def("open", &CacheManager::open)
       .def("is_open", &CacheManager::is_open)

@@ -12,6 +12,7 @@ CacheManager::CacheManager(std::vector<GroupConfig> groups, int num_state_slots,
     if (config.page_size <= 0) throw InvalidArgument("page size must be at least 1 token");
     if (config.num_pages <= 0) throw InvalidArgument("a group needs at least one page");
     if (config.window < 0) throw InvalidArgument("a window cannot be negative");
+    if (config.keep_first < 0) throw InvalidArgument("the count of kept first tokens cannot be negative");
     Group group;
     group.config = config;
     group.refs.assign(config.num_pages, 0);
@@ -219,7 +220,8 @@ bool CacheManager::admits(int length, int portion) const {
   for (const Group& group : groups_) {
     const int ps = group.config.page_size;
     int tokens = length;
-    if (group.config.window > 0) tokens = std::min(length, group.config.window + portion + ps);
+    if (group.config.window > 0)
+      tokens = std::min(length, group.config.window + portion + ps + (group.config.keep_first + ps - 1) / ps * ps);
     const int pages = (tokens + ps - 1) / ps;
     const int extra = kept_.empty() ? 0 : evictable_pages();
     if (pages > static_cast<int>(group.free.size()) + extra) return false;
@@ -292,8 +294,10 @@ void CacheManager::commit(int64_t request, int new_length) {
     // new_length - window + 1 on; pages wholly before that are out of every reach.
     int oldest = std::max(0, new_length - group.config.window + 1);
     int keep_from = oldest / group.config.page_size;
+    // pages that hold one of the first tokens every later query still sees are never given back
+    int kept_pages = (group.config.keep_first + group.config.page_size - 1) / group.config.page_size;
     std::vector<int32_t>& table = entry.tables[g];
-    for (int page = 0; page < keep_from && page < static_cast<int>(table.size()); ++page) {
+    for (int page = kept_pages; page < keep_from && page < static_cast<int>(table.size()); ++page) {
       if (table[page] < 0) continue;
       release_page(group, table[page]);
       table[page] = -1;
@@ -334,7 +338,8 @@ int64_t CacheManager::capacity_tokens() const {
     if (group.config.window > 0) {
       // A windowed group holds window + one portion; it bounds nothing as long as it
       // has the pages for the window itself and one page more.
-      int64_t least = (group.config.window + group.config.page_size - 1) / group.config.page_size + 1;
+      int64_t least = (group.config.window + group.config.page_size - 1) / group.config.page_size + 1 +
+                      (group.config.keep_first + group.config.page_size - 1) / group.config.page_size;
       if (group.config.num_pages < least) best = std::min<int64_t>(best, 0);
       continue;
     }

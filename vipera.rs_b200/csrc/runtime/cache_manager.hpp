@@ -5,8 +5,9 @@
 // whole or leaves nothing behind (crates/vipera-runtime/src/kv.rs:232-382), and
 // release returns every block of a sequence (kv.rs:539-561).  This manager keeps that
 // behaviour and adds two things the reference does not have: several groups of layers,
-// each with pages of its own and possibly a window after which pages are given back,
-// and a pool of fixed-size state slots, one per live request.
+// each with pages of its own and possibly a window after which pages are given back
+// (except the pages of the first `keep_first` tokens, which a windowed group may keep
+// visible for ever), and a pool of fixed-size state slots, one per live request.
 //
 // Reuse of prompt prefixes.  The reference parks a finished sequence's blocks and copies
 // whole blocks of a matching prefix into a new sequence (kv.rs:440-514; engine.rs:432-491:
@@ -42,6 +43,7 @@ struct GroupConfig {
   int page_size = 16;  // tokens per page
   int num_pages = 0;   // pages in this group's pool
   int window = 0;      // 0: every key is kept; w > 0: a query at p reads keys p-w+1 .. p
+  int keep_first = 0;  // with a window: keys 0 .. keep_first-1 stay visible to every later query
 };
 
 struct GroupStats {

@@ -71,4 +71,4 @@ def write_random_model(model_dir: str, config_dict: dict, seed: int, dtype="bflo
     config = arch.config_from_dict(config_dict)
     spec = arch.model_spec(config)
     out = config.to_dict() if hasattr(config, "to_dict") else dict(config_dict)
-    write_model_folder(model_dir, out, model_schema(spec), seed, parse_dtype(dtype))
+    write_model_folder(model_dir, out, model_schema(spec), seed, parse_dtype(dtype), stored_name=arch.stored_name)

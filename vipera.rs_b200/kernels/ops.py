@@ -19,6 +19,9 @@ from ..errors import InternalError, InvalidArgumentError, UnsupportedError
 
 F32, BF16 = 0, 1
 EPI_STORE, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2
+EPI_GATED = EPI_SWIGLU   # the gated unit over interleaved gate and up rows; its activation is an argument
+ACT_SILU, ACT_GELU_TANH = 0, 1
+ACTIVATIONS = {"silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH}
 ROPE_NONE, ROPE_NEOX, ROPE_INTERLEAVED = 0, 1, 2
 SAMPLE_OK, SAMPLE_NO_FINITE, SAMPLE_NO_MASS, SAMPLE_NEEDS_HOST = 0, 1, 2, 3
 
@@ -89,11 +92,11 @@ class KernelProfile:
         "embed": "embed", "rmsnorm": "norm", "rope_cache": "rope_kv",
         "gemm_tc": "proj", "gemm_tc_rope": "proj", "gemv_small": "proj", "gemm_simt": "proj",
         "attention": "attention", "attention_prefill": "attention", "attention_prefill_tc": "attention",
-        "attention_decode": "attention",
+        "attention_decode": "attention", "mlstm": "recurrence",
         "argmax": "sample", "sample": "sample", "apply_penalties": "sample", "feed_tokens": "sample",
         "logprobs": "sample",
     }
-    ORDER = ("proj", "attention", "norm", "rope_kv", "embed", "sample", "other")
+    ORDER = ("proj", "attention", "recurrence", "norm", "rope_kv", "embed", "sample", "other")
 
     def __init__(self):
         self._events = []
@@ -231,9 +234,19 @@ def rope_cache(qkv: torch.Tensor, q_out: torch.Tensor, *, num_heads: int, num_kv
                positions: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], style: int,
                k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor],
                token_seq: Optional[torch.Tensor], block_table: Optional[torch.Tensor], page_size: int,
-               write_cache: bool) -> None:
+               write_cache: bool, value_dim: Optional[int] = None, rot_dims: Optional[int] = None) -> None:
     """Rotate q and k of a float32 [tokens, (heads + 2 kv_heads) * d] product; write q to
-    q_out [tokens, heads * d] and k, v into their cache pages."""
+    q_out [tokens, heads * d] and k, v into their cache pages.  ``rot_dims`` (default d): only
+    the first that many values of a head turn, with tables of width rot_dims/2; ``value_dim``
+    (default d): a value row's size, the product then being [tokens, (heads + kv_heads) * d +
+    kv_heads * value_dim]."""
+    value_dim = head_dim if value_dim is None else int(value_dim)
+    rot_dims = head_dim if rot_dims is None else int(rot_dims)
+    if value_dim != head_dim or rot_dims != head_dim:
+        return _rope_cache_partial(qkv, q_out, num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim,
+                                   value_dim=value_dim, rot_dims=rot_dims, positions=positions, cos=cos, sin=sin,
+                                   style=style, k_pool=k_pool, v_pool=v_pool, token_seq=token_seq,
+                                   block_table=block_table, page_size=page_size, write_cache=write_cache)
     fn = _function("rope_cache", "vipera_rope_cache",
                    [_c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void, _c_void, _c_int,
                     _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_void])
@@ -259,13 +272,46 @@ def rope_cache(qkv: torch.Tensor, q_out: torch.Tensor, *, num_heads: int, num_kv
               _stream()), "rope_cache")
 
 
+def _rope_cache_partial(qkv, q_out, *, num_heads, num_kv_heads, head_dim, value_dim, rot_dims, positions, cos, sin,
+                        style, k_pool, v_pool, token_seq, block_table, page_size, write_cache) -> None:
+    fn = _function("rope_cache", "vipera_rope_cache_partial",
+                   [_c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void, _c_void,
+                    _c_int, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_void])
+    count = qkv.shape[0]
+    if qkv.shape[1] != (num_heads + num_kv_heads) * head_dim + num_kv_heads * value_dim:
+        raise InvalidArgumentError("rope_cache: qkv width does not match the head counts and sizes")
+    if q_out.shape[0] != count or q_out.shape[1] != num_heads * head_dim:
+        raise InvalidArgumentError("rope_cache: q_out has the wrong shape")
+    if rot_dims % 2 or not 0 <= rot_dims <= head_dim:
+        raise InvalidArgumentError("rope_cache: the rotated values must be an even count within the head")
+    if style != ROPE_NONE and rot_dims:
+        if cos is None or sin is None or cos.shape[1] != rot_dims // 2 or sin.shape != cos.shape:
+            raise InvalidArgumentError("rope_cache: cos/sin tables of width rot_dims/2 are needed")
+    if write_cache:
+        if k_pool is None or v_pool is None or k_pool.dtype != q_out.dtype or v_pool.dtype != q_out.dtype:
+            raise InvalidArgumentError("rope_cache: cache pools must have the activation dtype")
+        if k_pool.shape[1:] != (page_size, num_kv_heads, head_dim) or \
+                v_pool.shape[1:] != (page_size, num_kv_heads, value_dim):
+            raise InvalidArgumentError("rope_cache: cache pools must be [pages, page_size, kv_heads, d] and "
+                                       "[pages, page_size, kv_heads, value size]")
+    width = 0 if block_table is None else block_table.shape[1]
+    _check(fn(_gpu(qkv, "qkv", torch.float32), _gpu(q_out, "q_out"), dtype_code(q_out.dtype), count,
+              num_heads, num_kv_heads, head_dim, value_dim, rot_dims, _gpu(positions, "positions", torch.int32),
+              _opt(cos, "cos", torch.float32), _opt(sin, "sin", torch.float32), style,
+              _opt(k_pool, "k_pool"), _opt(v_pool, "v_pool"), _opt(token_seq, "token_seq", torch.int32),
+              _opt(block_table, "block_table", torch.int32), width, page_size, 1 if write_cache else 0,
+              _stream()), "rope_cache")
+
+
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_STORE,
               bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-              resid: Optional[torch.Tensor] = None) -> None:
-    """a[M, K] times w[N, K] transposed, on the CUDA cores with float32 accumulation."""
-    fn = _function("gemm_simt", "vipera_gemm_simt",
+              resid: Optional[torch.Tensor] = None, activation: int = ACT_SILU) -> None:
+    """a[M, K] times w[N, K] transposed, on the CUDA cores with float32 accumulation.  ``bias``
+    counts in every ending (for the gated unit it is interleaved like the rows);
+    ``activation`` is the gated unit's."""
+    fn = _function("gemm_simt", "vipera_gemm_simt_act",
                    [_c_void, _c_int, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void, _c_int,
-                    _c_void, _c_void])
+                    _c_void, _c_int, _c_void])
     m, k = a.shape
     n = w.shape[0]
     if w.shape[1] != k:
@@ -274,15 +320,15 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_STORE,
     _check(fn(_gpu(a, "a"), dtype_code(a.dtype), _gpu(w, "w"), dtype_code(w.dtype), m, n, k, epilogue,
               _opt(bias, "bias", torch.float32), _opt(out, "out"),
               dtype_code(out.dtype) if out is not None else F32, _opt(resid, "resid", torch.float32),
-              _stream()), "gemm_simt")
+              int(activation), _stream()), "gemm_simt")
 
 
 def _check_gemm_outputs(m, n, epilogue, bias, out, resid) -> None:
+    if bias is not None and bias.numel() != n:
+        raise InvalidArgumentError("gemm: bias must have one value per row of the matrix")
     if epilogue == EPI_STORE:
         if out is None or tuple(out.shape) != (m, n):
             raise InvalidArgumentError(f"gemm: out must be [{m}, {n}]")
-        if bias is not None and bias.numel() != n:
-            raise InvalidArgumentError("gemm: bias must have one value per output column")
     elif epilogue == EPI_RESIDUAL:
         if resid is None or tuple(resid.shape) != (m, n):
             raise InvalidArgumentError(f"gemm: resid must be [{m}, {n}]")
@@ -297,25 +343,32 @@ def _check_gemm_outputs(m, n, epilogue, bias, out, resid) -> None:
 
 def attention(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, *,
               token_seq: torch.Tensor, positions: torch.Tensor, block_table: torch.Tensor,
-              num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: int = 0) -> None:
-    """Causal grouped-query attention of every token of the step over its request's pages."""
+              num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: int = 0,
+              value_dim: Optional[int] = None, keep_first: int = 0, sink: bool = False) -> None:
+    """Causal grouped-query attention of every token of the step over its request's pages.
+    ``value_dim``: a value row's size (default d); ``keep_first``: with a window, that many
+    first keys stay visible; ``sink``: one is added to the softmax's denominator."""
     fn = _function("attention", "vipera_attention",
                    [_c_void, _c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int,
-                    _c_int, _c_int, _c_int, _c_float, _c_int, _c_void])
+                    _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_void])
     count = q.shape[0]
-    if head_dim % 16 or head_dim > 256:
-        raise UnsupportedError(f"attention: head size {head_dim} is not a multiple of 16 up to 256")
-    if q.shape[1] != num_heads * head_dim or out.shape != q.shape or out.dtype != q.dtype:
-        raise InvalidArgumentError("attention: q and out must be [tokens, heads * d] of one dtype")
-    if k_pool.dtype != q.dtype or v_pool.shape != k_pool.shape:
+    value_dim = head_dim if value_dim is None else int(value_dim)
+    for size in (head_dim, value_dim):
+        if size % 8 or size > 256:
+            raise UnsupportedError(f"attention: head size {size} is not a multiple of 8 up to 256")
+    if q.shape[1] != num_heads * head_dim or tuple(out.shape) != (count, num_heads * value_dim) or out.dtype != q.dtype:
+        raise InvalidArgumentError("attention: q must be [tokens, heads * d] and out [tokens, heads * value size], of one dtype")
+    if k_pool.dtype != q.dtype or v_pool.dtype != q.dtype or v_pool.shape[:3] != k_pool.shape[:3]:
         raise InvalidArgumentError("attention: cache pools must match q's dtype and each other")
     page_size = k_pool.shape[1]
-    if k_pool.shape[2:] != (num_kv_heads, head_dim):
-        raise InvalidArgumentError("attention: cache pools must be [pages, page_size, kv_heads, d]")
+    if k_pool.shape[2:] != (num_kv_heads, head_dim) or v_pool.shape[3] != value_dim:
+        raise InvalidArgumentError("attention: cache pools must be [pages, page_size, kv_heads, d] and "
+                                   "[pages, page_size, kv_heads, value size]")
     _check(fn(_gpu(q, "q"), _gpu(out, "out"), dtype_code(q.dtype), _gpu(k_pool, "k_pool"), _gpu(v_pool, "v_pool"),
               _gpu(token_seq, "token_seq", torch.int32), _gpu(positions, "positions", torch.int32),
               _gpu(block_table, "block_table", torch.int32), block_table.shape[1], page_size, count,
-              num_heads, num_kv_heads, head_dim, float(scale), int(window or 0), _stream()), "attention")
+              num_heads, num_kv_heads, head_dim, value_dim, float(scale), int(window or 0),
+              int(keep_first or 0) if window else 0, 1 if sink else 0, _stream()), "attention")
 
 
 # ----------------------------------------------------------------------------------------
@@ -813,6 +866,77 @@ def gemv_small(w: torch.Tensor, *, a: Optional[torch.Tensor] = None, x: Optional
         p.out_dtype = dtype_code(out.dtype) if out is not None else F32
         p.resid = _opt(resid, "resid", torch.float32)
     _check(fn(ctypes.byref(p), _stream()), "gemv_small")
+
+
+# ----------------------------------------------------------------------------------------
+# the matrix-memory cell (mLSTM)
+# ----------------------------------------------------------------------------------------
+class _MlstmParams(ctypes.Structure):
+    _fields_ = [
+        ("proj", _c_void), ("proj_width", _c_int),
+        ("q_off", _c_int), ("k_off", _c_int), ("v_off", _c_int), ("g_off", _c_int), ("i_off", _c_int), ("f_off", _c_int),
+        ("heads", _c_int), ("dim", _c_int), ("vdim", _c_int), ("tile", _c_int), ("num_entries", _c_int),
+        ("q_scale", _c_float), ("gate_cap", _c_float), ("denom_eps", _c_float),
+        ("entry_starts", _c_void), ("state_slots", _c_void), ("fresh", _c_void), ("state", _c_void),
+        ("state_stride", ctypes.c_longlong), ("o_raw", _c_void), ("nm_scratch", _c_void),
+    ]
+
+
+_mlstm_checked = False
+
+
+def mlstm_state_floats(heads: int, dim: int, vdim: int) -> int:
+    """Floats of one request's state row: S [heads, d, dv], n [heads, d], m [heads], rounded up
+    to a multiple of four (the same rule as the kernel file's)."""
+    return (heads * (dim * vdim + dim + 1) + 3) // 4 * 4
+
+
+def mlstm_takes(dim: int, vdim: int) -> bool:
+    fn = getattr(load_kernel_library("mlstm"), "vipera_mlstm_tile")
+    fn.argtypes, fn.restype = [_c_int, _c_int], _c_int
+    return fn(int(dim), int(vdim)) > 0
+
+
+def mlstm(proj: torch.Tensor, *, offsets, heads: int, dim: int, vdim: int, q_scale: float, gate_cap: float,
+          denom_eps: float, entry_starts: torch.Tensor, state_slots: torch.Tensor, fresh: torch.Tensor,
+          token_entry: torch.Tensor, num_entries: int, single: bool, state: torch.Tensor, o_raw: torch.Tensor,
+          nm_scratch: torch.Tensor, norm_weight: torch.Tensor, norm_eps: float, out: torch.Tensor) -> None:
+    """The mLSTM cell over a step.  ``proj`` is the float32 product [tokens, width] that holds q, k,
+    v, the output gate and the two gates' pre-activations at ``offsets`` (q, k, v, g, i, f);
+    ``state`` is [slots, mlstm_state_floats]; ``out`` [tokens, heads * vdim] receives the cell's
+    output after the head norm (times ``norm_weight``) and the output gate.  ``single`` promises
+    that every entry brings one token."""
+    global _mlstm_checked
+    fn = _function("mlstm", "vipera_mlstm",
+                   [ctypes.POINTER(_MlstmParams), _c_int, _c_int, _c_void, _c_float, _c_void, _c_int, _c_void, _c_void])
+    if not _mlstm_checked:
+        size = _function("mlstm", "vipera_mlstm_params_size", [])()
+        if size != ctypes.sizeof(_MlstmParams):
+            raise InternalError(f"mlstm: parameter block is {ctypes.sizeof(_MlstmParams)} bytes here, {size} in the kernel")
+        _mlstm_checked = True
+    tokens, width = proj.shape
+    if tuple(out.shape) != (tokens, heads * vdim):
+        raise InvalidArgumentError("mlstm: out must be [tokens, heads * value size]")
+    if state.dim() != 2 or state.shape[1] != mlstm_state_floats(heads, dim, vdim):
+        raise InvalidArgumentError("mlstm: state rows have the wrong size")
+    if o_raw.numel() < tokens * heads * vdim or nm_scratch.numel() < num_entries * heads * (dim + 1):
+        raise InvalidArgumentError("mlstm: scratch buffers are too small")
+    if norm_weight.numel() != heads * vdim:
+        raise InvalidArgumentError("mlstm: the head norm's weight must have heads * value size values")
+    p = _MlstmParams()
+    p.proj, p.proj_width = _gpu(proj, "proj", torch.float32), width
+    p.q_off, p.k_off, p.v_off, p.g_off, p.i_off, p.f_off = (int(x) for x in offsets)
+    p.heads, p.dim, p.vdim, p.tile, p.num_entries = heads, dim, vdim, 0, int(num_entries)
+    p.q_scale, p.gate_cap, p.denom_eps = float(q_scale), float(gate_cap), float(denom_eps)
+    p.entry_starts = _gpu(entry_starts, "entry_starts", torch.int32)
+    p.state_slots = _gpu(state_slots, "state_slots", torch.int32)
+    p.fresh = _gpu(fresh, "fresh", torch.int32)
+    p.state, p.state_stride = _gpu(state, "state", torch.float32), state.shape[1]
+    p.o_raw = _gpu(o_raw, "o_raw", torch.float32)
+    p.nm_scratch = _gpu(nm_scratch, "nm_scratch", torch.float32)
+    _check(fn(ctypes.byref(p), tokens, 1 if single else 0, _gpu(norm_weight, "norm_weight", torch.float32),
+              float(norm_eps), _gpu(out, "out"), dtype_code(out.dtype), _gpu(token_entry, "token_entry", torch.int32),
+              _stream()), "mlstm", kernels=2)
 
 
 def kernel_status_word(device) -> torch.Tensor:

@@ -1,6 +1,6 @@
 """Parts a decoder is put together from.  Importing this package registers the built-in
-kinds: ``rmsnorm``; ``rope_neox``, ``rope_interleaved`` and ``none``; ``gqa_attention``; ``swiglu``; ``prenorm``."""
-from . import attention, block, mlp, norm, rotary  # noqa: F401  (registration)
+kinds: ``rmsnorm``; ``rope_neox``, ``rope_interleaved`` and ``none``; ``gqa_attention`` and ``mlstm``; ``swiglu`` (also ``gated_mlp``); ``prenorm`` and ``prenorm_mixer``."""
+from . import attention, block, mlp, mlstm, norm, rotary  # noqa: F401  (registration)
 from .base import (
     FeedForward,
     FixedState,

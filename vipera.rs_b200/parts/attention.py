@@ -25,7 +25,12 @@ from .linear import Linear, NormedInput
 class GQAttention(Mixer):
     """params: hidden_size, num_heads, num_kv_heads, head_dim, qkv_bias, window (None or a
     count of keys), softmax_scale, position (a PartSpec of a position encoding) and,
-    optionally, ``projection_names`` (defaults q_proj, k_proj, v_proj, o_proj)."""
+    optionally, ``projection_names`` (defaults q_proj, k_proj, v_proj, o_proj), ``value_dim`` (the
+    size of a value row and of a head's output, default head_dim), ``keep_first`` (with a window:
+    the first that many keys of a request stay visible to every later query, at their true
+    positions) and ``sink`` (true: a key of score 0 without a value joins every softmax, which
+    adds one to its denominator).  A position encoding may turn only the first values of a head
+    (its ``rot_dims``)."""
 
     kernels = ("rope_cache", "attention", "attention_mma", "attention_tc")
     takes_lazy_input = True
@@ -37,18 +42,20 @@ class GQAttention(Mixer):
     @classmethod
     def schema(cls, params, prefix):
         hidden, d = params["hidden_size"], params["head_dim"]
+        dv = params.get("value_dim") or d
         q_width, kv_width = params["num_heads"] * d, params["num_kv_heads"] * d
+        v_width = params["num_kv_heads"] * dv
         qn, kn, vn, on = cls._names(params)
         schema = {
             f"{prefix}.{qn}.weight": TensorSpec((q_width, hidden)),
             f"{prefix}.{kn}.weight": TensorSpec((kv_width, hidden)),
-            f"{prefix}.{vn}.weight": TensorSpec((kv_width, hidden)),
-            f"{prefix}.{on}.weight": TensorSpec((hidden, q_width)),
+            f"{prefix}.{vn}.weight": TensorSpec((v_width, hidden)),
+            f"{prefix}.{on}.weight": TensorSpec((hidden, params["num_heads"] * dv)),
         }
         if params.get("qkv_bias", False):
             schema[f"{prefix}.{qn}.bias"] = TensorSpec((q_width,), init="bias")
             schema[f"{prefix}.{kn}.bias"] = TensorSpec((kv_width,), init="bias")
-            schema[f"{prefix}.{vn}.bias"] = TensorSpec((kv_width,), init="bias")
+            schema[f"{prefix}.{vn}.bias"] = TensorSpec((v_width,), init="bias")
         return schema
 
     def __init__(self, params, prefix, tensors, dtype, device):
@@ -57,11 +64,14 @@ class GQAttention(Mixer):
         self.num_heads = int(params["num_heads"])
         self.num_kv_heads = int(params["num_kv_heads"])
         self.head_dim = int(params["head_dim"])
+        self.value_dim = int(params.get("value_dim") or self.head_dim)
         self.window = params.get("window")
+        self.keep_first = int(params.get("keep_first") or 0) if self.window else 0
+        self.sink = bool(params.get("sink", False))
         self.scale = float(params["softmax_scale"])
-        if self.head_dim % 16 or self.head_dim > 256:
-            raise UnsupportedError(
-                f"head size {self.head_dim}: the attention kernels take multiples of 16 up to 256")
+        for size in (self.head_dim, self.value_dim):
+            if size % 8 or size > 256:
+                raise UnsupportedError(f"head size {size}: the attention kernels take multiples of 8 up to 256")
         if self.num_heads % self.num_kv_heads:
             raise UnsupportedError("the number of heads must be a multiple of the number of KV heads")
         qn, kn, vn, on = self._names(params)
@@ -73,12 +83,17 @@ class GQAttention(Mixer):
         self.out = Linear(tensors[f"{prefix}.{on}.weight"], dtype, device)
         position = params["position"]
         self.position = POSITION_ENCODINGS.find(position.kind)(position.params, prefix, tensors, dtype, device)
+        self.rot_dims = int(getattr(self.position, "rot_dims", self.head_dim))
+        # The fused endings and the tensor-core attention kernels know the common form only: values as
+        # long as keys, whole heads that turn, a plain window, a plain softmax.
+        self.common_form = (self.value_dim == self.head_dim and self.rot_dims == self.head_dim
+                            and not self.keep_first and not self.sink and self.head_dim % 16 == 0)
 
     def kernel_families(self):
         # the tensor-core attention kernels serve bfloat16 with head sizes 64 and 128; everything
         # else runs through the general kernel
         own = ["rope_cache", "attention"]
-        if self.dtype == torch.bfloat16 and self.head_dim in (64, 128):
+        if self.dtype == torch.bfloat16 and self.head_dim in (64, 128) and self.common_form:
             own.append("attention_mma")
             if self.head_dim in ops.TC_ATTENTION_HEAD_DIMS:
                 own.append("attention_tc")
@@ -92,23 +107,26 @@ class GQAttention(Mixer):
 
     @classmethod
     def cache_request_for(cls, params):
-        return PagedKV(int(params["num_kv_heads"]), int(params["head_dim"]), params.get("window"))
+        return PagedKV(int(params["num_kv_heads"]), int(params["head_dim"]), params.get("window"),
+                       value_dim=int(params.get("value_dim") or params["head_dim"]),
+                       keep_first=int(params.get("keep_first") or 0))
 
     @classmethod
     def workspace_bytes(cls, params, tokens, element_bytes):
+        dv = params.get("value_dim") or params["head_dim"]
         q_width = params["num_heads"] * params["head_dim"]
-        qkv_width = q_width + 2 * params["num_kv_heads"] * params["head_dim"]
+        qkv_width = q_width + params["num_kv_heads"] * (params["head_dim"] + dv)
         # q and the attention's output in the run's type, and the 32-bit q/k/v product of the unfused route
-        return tokens * (2 * q_width * element_bytes + qkv_width * 4)
+        return tokens * ((q_width + params["num_heads"] * dv) * element_bytes + qkv_width * 4)
 
     def forward(self, ctx, h, residual, cache, writes_cache):
         count = ctx.num_tokens
-        heads, kv_heads, d = self.num_heads, self.num_kv_heads, self.head_dim
+        heads, kv_heads, d, dv = self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim
         ws = ctx.workspace
         q = ws.get("attention.q", (count, heads * d), ctx.dtype)
         table = ctx.block_tables[cache.group]
         style = self.position.style
-        if self.qkv.takes_small(count) and style in (ops.ROPE_NONE, ops.ROPE_NEOX):
+        if self.common_form and self.qkv.takes_small(count) and style in (ops.ROPE_NONE, ops.ROPE_NEOX):
             # few tokens: one kernel for norm, q/k/v product, bias, rotation and cache write
             cos, sin = self.position.tables()
             rope = dict(num_heads=heads, num_kv_heads=kv_heads, head_dim=d, style=style, positions=ctx.positions,
@@ -124,7 +142,7 @@ class GQAttention(Mixer):
             self._attend(ctx, q, mixed, cache, table)
             self.out(ctx, mixed, epilogue=ops.EPI_RESIDUAL, resid=residual)
             return
-        if (ctx.dtype == torch.bfloat16 and style in (ops.ROPE_NONE, ops.ROPE_NEOX)
+        if (self.common_form and ctx.dtype == torch.bfloat16 and style in (ops.ROPE_NONE, ops.ROPE_NEOX)
                 and self.qkv.tensor_core
                 and ops.gemm_tc_rope_takes(count, self.qkv.out_features, self.qkv.in_features, d)):
             # many tokens: the tensor-core product ends with bias, rotation and cache write
@@ -138,7 +156,7 @@ class GQAttention(Mixer):
             self._attend(ctx, q, mixed, cache, table)
             self.out(ctx, mixed, epilogue=ops.EPI_RESIDUAL, resid=residual)
             return
-        qkv = ws.get("attention.qkv", (count, (heads + 2 * kv_heads) * d), torch.float32)
+        qkv = ws.get("attention.qkv", (count, (heads + kv_heads) * d + kv_heads * dv), torch.float32)
         self.qkv(ctx, h, epilogue=ops.EPI_STORE, out=qkv)
         if style is None:
             # An encoding the fused kernel does not know: the part applies it to the 32-bit
@@ -152,8 +170,8 @@ class GQAttention(Mixer):
         ops.rope_cache(qkv, q, num_heads=heads, num_kv_heads=kv_heads, head_dim=d,
                        positions=ctx.positions, cos=cos, sin=sin, style=style,
                        k_pool=cache.k, v_pool=cache.v, token_seq=ctx.token_entry, block_table=table,
-                       page_size=cache.page_size, write_cache=writes_cache)
-        mixed = ws.get("attention.out", (count, heads * d), ctx.dtype)
+                       page_size=cache.page_size, write_cache=writes_cache, value_dim=dv, rot_dims=self.rot_dims)
+        mixed = ws.get("attention.out", (count, heads * dv), ctx.dtype)
         self._attend(ctx, q, mixed, cache, table)
         self.out(ctx, mixed, epilogue=ops.EPI_RESIDUAL, resid=residual)
 
@@ -163,7 +181,7 @@ class GQAttention(Mixer):
         kernel otherwise; in every other case the general kernel."""
         heads, kv_heads, d = self.num_heads, self.num_kv_heads, self.head_dim
         window = self.window or 0
-        if ctx.dtype == torch.bfloat16 and d in ops.MMA_HEAD_DIMS:
+        if ctx.dtype == torch.bfloat16 and d in ops.MMA_HEAD_DIMS and self.common_form:
             if ctx.all_single:
                 chunk, splits = ops.decode_splits(ctx.num_entries, kv_heads, max(ctx.max_kv_len, 1),
                                                   ops.sm_count(q.device))
@@ -194,7 +212,8 @@ class GQAttention(Mixer):
             return
         ops.attention(q, mixed, cache.k, cache.v, token_seq=ctx.token_entry, positions=ctx.positions,
                       block_table=table, num_heads=heads, num_kv_heads=kv_heads, head_dim=d,
-                      scale=self.scale, window=window)
+                      scale=self.scale, window=window, value_dim=self.value_dim, keep_first=self.keep_first,
+                      sink=self.sink)
 
 
 MIXERS.register("gqa_attention", GQAttention)

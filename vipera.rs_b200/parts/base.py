@@ -37,6 +37,8 @@ class PagedKV:
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None  # None: all keys; w: a query at p reads p-w+1 .. p
+    value_dim: Optional[int] = None  # size of a value row where it differs from a key row's
+    keep_first: int = 0           # with a window: keys 0 .. keep_first-1 stay visible to every later query
 
 
 @dataclass(frozen=True)
@@ -48,14 +50,17 @@ class FixedState:
 
 
 class PagedKVView:
-    """The pages of one cache slot: ``k`` and ``v`` are [pages, page_size, kv_heads, d]."""
+    """The pages of one cache slot: ``k`` is [pages, page_size, kv_heads, d] and ``v`` the same
+    with the value size in the last place."""
 
-    def __init__(self, group: int, k: torch.Tensor, v: torch.Tensor, page_size: int, window: Optional[int]):
+    def __init__(self, group: int, k: torch.Tensor, v: torch.Tensor, page_size: int, window: Optional[int],
+                 keep_first: int = 0):
         self.group = group
         self.k = k
         self.v = v
         self.page_size = page_size
         self.window = window
+        self.keep_first = keep_first
 
 
 class StateView:

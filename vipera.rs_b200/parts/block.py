@@ -102,4 +102,15 @@ class PreNormBlock(Block):
         self.ffn.forward(ctx, self._input(self.ffn, h), residual)
 
 
+class PreNormMixerBlock(Block):
+    """A layer without a feed-forward: ``x += mixer(norm(x))`` and nothing more."""
+
+    roles = {"mixer_norm": NORMS, "mixer": MIXERS}
+
+    def forward(self, ctx, residual, cache, writes_cache):
+        h = NormedInput(ctx, self.mixer_norm, residual)
+        self.mixer.forward(ctx, self._input(self.mixer, h), residual, cache, writes_cache)
+
+
 BLOCKS.register("prenorm", PreNormBlock)
+BLOCKS.register("prenorm_mixer", PreNormMixerBlock)

@@ -100,11 +100,19 @@ class Linear:
         return known
 
     def __call__(self, ctx, a, *, epilogue: int = ops.EPI_STORE,
-                 out: Optional[torch.Tensor] = None, resid: Optional[torch.Tensor] = None) -> None:
-        """``a`` is a tensor [tokens, K] in the run dtype, or a NormedInput."""
-        bias = self.bias if epilogue == ops.EPI_STORE else None
+                 out: Optional[torch.Tensor] = None, resid: Optional[torch.Tensor] = None,
+                 activation: int = ops.ACT_SILU) -> None:
+        """``a`` is a tensor [tokens, K] in the run dtype, or a NormedInput.  A bias counts in
+        every ending (in the gated unit it is interleaved like the rows); ``activation`` is the
+        gated unit's."""
+        bias = self.bias
         lazy = a if isinstance(a, NormedInput) else None
         tokens = lazy.num_rows if lazy is not None else a.shape[0]
+        if (bias is not None and epilogue != ops.EPI_STORE) or activation != ops.ACT_SILU:
+            # the tensor-core kernels' endings know a bias with a plain store and silu only
+            ops.gemm_simt(lazy.tensor() if lazy is not None else a, self.weight, epilogue=epilogue, bias=bias,
+                          out=out, resid=resid, activation=activation)
+            return
         if self.takes_small(tokens):
             if lazy is not None and lazy.fusable and lazy._tensor is None:
                 ops.gemv_small(self.weight, x=lazy.residual, norm_weight=lazy.norm.weight, eps=lazy.norm.eps,

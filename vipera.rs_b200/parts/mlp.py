@@ -11,6 +11,7 @@ from __future__ import annotations
 import torch
 
 from ..config.registry import FEED_FORWARDS
+from ..errors import UnsupportedError
 from ..kernels import ops
 from ..weights import TensorSpec
 from .base import FeedForward
@@ -18,8 +19,10 @@ from .linear import Linear, interleave_gate_up
 
 
 class SwiGLU(FeedForward):
-    """params: hidden_size, intermediate_size and, optionally, ``projection_names``
-    (defaults gate_proj, up_proj, down_proj)."""
+    """A gated feed-forward, ``down(act(gate(h)) * up(h))``.  params: hidden_size,
+    intermediate_size and, optionally, ``projection_names`` (defaults gate_proj, up_proj,
+    down_proj), ``activation`` (``silu``, the default, or ``gelu_tanh``) and ``bias`` (all three
+    projections then have one, ``<name>.bias``).  Registered as ``swiglu`` and ``gated_mlp``."""
 
     takes_lazy_input = True
 
@@ -31,11 +34,16 @@ class SwiGLU(FeedForward):
     def schema(cls, params, prefix):
         hidden, inter = params["hidden_size"], params["intermediate_size"]
         gate, up, down = cls._names(params)
-        return {
+        schema = {
             f"{prefix}.{gate}.weight": TensorSpec((inter, hidden)),
             f"{prefix}.{up}.weight": TensorSpec((inter, hidden)),
             f"{prefix}.{down}.weight": TensorSpec((hidden, inter)),
         }
+        if params.get("bias", False):
+            schema[f"{prefix}.{gate}.bias"] = TensorSpec((inter,), init="bias")
+            schema[f"{prefix}.{up}.bias"] = TensorSpec((inter,), init="bias")
+            schema[f"{prefix}.{down}.bias"] = TensorSpec((hidden,), init="bias")
+        return schema
 
     @classmethod
     def workspace_bytes(cls, params, tokens, element_bytes):
@@ -46,17 +54,28 @@ class SwiGLU(FeedForward):
         self.hidden = int(params["hidden_size"])
         self.inter = int(params["intermediate_size"])
         gate, up, down = self._names(params)
+        name = str(params.get("activation", "silu"))
+        if name not in ops.ACTIVATIONS:
+            raise UnsupportedError(f"activation {name!r}; the gated unit knows: " + ", ".join(sorted(ops.ACTIVATIONS)))
+        self.activation = ops.ACTIVATIONS[name]
         fused = interleave_gate_up(tensors[f"{prefix}.{gate}.weight"], tensors[f"{prefix}.{up}.weight"])
-        self.gate_up = Linear(fused, dtype, device)
-        self.down = Linear(tensors[f"{prefix}.{down}.weight"], dtype, device)
+        fused_bias = down_bias = None
+        if params.get("bias", False):
+            # the bias of the interleaved rows, interleaved the same way
+            fused_bias = interleave_gate_up(tensors[f"{prefix}.{gate}.bias"].to(torch.float32)[:, None],
+                                            tensors[f"{prefix}.{up}.bias"].to(torch.float32)[:, None]).reshape(-1)
+            down_bias = tensors[f"{prefix}.{down}.bias"]
+        self.gate_up = Linear(fused, dtype, device, bias=fused_bias)
+        self.down = Linear(tensors[f"{prefix}.{down}.weight"], dtype, device, bias=down_bias)
 
     def kernel_families(self):
         return tuple(dict.fromkeys(self.gate_up.kernel_families() + self.down.kernel_families()))
 
     def forward(self, ctx, h, residual):
         act = ctx.workspace.get("swiglu.act", (ctx.num_tokens, self.inter), ctx.dtype)
-        self.gate_up(ctx, h, epilogue=ops.EPI_SWIGLU, out=act)
+        self.gate_up(ctx, h, epilogue=ops.EPI_GATED, out=act, activation=self.activation)
         self.down(ctx, act, epilogue=ops.EPI_RESIDUAL, resid=residual)
 
 
 FEED_FORWARDS.register("swiglu", SwiGLU)
+FEED_FORWARDS.register("gated_mlp", SwiGLU)

@@ -9,9 +9,12 @@ the same head size and base.  Tables live as long as a part holds them.
 """
 from __future__ import annotations
 
+import math
 import weakref
 
 import torch
+
+from ..errors import InvalidArgumentError
 
 from ..config.registry import POSITION_ENCODINGS
 from ..kernels import ops
@@ -27,9 +30,34 @@ class _Tables:
 _TABLES = weakref.WeakValueDictionary()
 
 
-def rotary_tables(head_dim: int, theta: float, max_positions: int, device) -> _Tables:
-    """cos and sin, each float32 [max_positions, head_dim / 2], on ``device``."""
-    key = (head_dim, float(theta), max_positions, str(device))
+def yarn_blend(inverse: torch.Tensor, dims: int, theta: float, scaling: dict):
+    """YaRN scaling of the frequencies ``inverse`` [dims/2] of a rotation over ``dims`` values:
+    (blended frequencies, stretch of cos and sin).  ``scaling`` holds ``factor``, ``original``
+    (the length the model first saw), and ``fast`` and ``slow``, the numbers of full turns within
+    that length above which a pair keeps its frequency and below which it is slowed by the
+    factor; pairs in between are blended by a linear ramp over the pair index.  The pair that
+    makes t turns within the original length has index dims ln(original / (2 pi t)) / (2 ln theta).
+    Both tables are stretched by 0.1 ln(factor) + 1."""
+    factor, original = float(scaling["factor"]), float(scaling["original"])
+    if not (factor > 0 and original > 0 and float(scaling["fast"]) > 0 and float(scaling["slow"]) > 0):
+        raise InvalidArgumentError("YaRN scaling needs positive factor, original, fast and slow")
+
+    def pair_of(turns: float) -> float:
+        return dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
+
+    low = max(math.floor(pair_of(float(scaling["fast"]))), 0)
+    high = min(math.ceil(pair_of(float(scaling["slow"]))), dims - 1)
+    index = torch.arange(dims // 2, dtype=torch.float64)
+    ramp = torch.clamp((index - low) / max(high - low, 0.001), 0.0, 1.0).to(torch.float32)
+    blended = inverse / torch.tensor(factor, dtype=torch.float32) * ramp + inverse * (1.0 - ramp)
+    return blended, 0.1 * math.log(factor) + 1.0
+
+
+def rotary_tables(head_dim: int, theta: float, max_positions: int, device, scaling=None) -> _Tables:
+    """cos and sin, each float32 [max_positions, head_dim / 2], on ``device``; ``head_dim`` is the
+    count of values that turn.  ``scaling``: None, or the YaRN constants (see ``yarn_blend``)."""
+    frozen = None if not scaling else tuple(sorted((str(k), float(v)) for k, v in scaling.items()))
+    key = (head_dim, float(theta), max_positions, str(device), frozen)
     cached = _TABLES.get(key)
     if cached is not None:
         return cached
@@ -37,15 +65,23 @@ def rotary_tables(head_dim: int, theta: float, max_positions: int, device) -> _T
     index = torch.arange(half, dtype=torch.float32)
     exponent = 2.0 * index / torch.tensor(float(head_dim), dtype=torch.float32)
     inverse = 1.0 / torch.pow(torch.tensor(float(theta), dtype=torch.float32), exponent)
+    stretch = 1.0
+    if scaling:
+        inverse, stretch = yarn_blend(inverse, head_dim, float(theta), scaling)
     position = torch.arange(max_positions, dtype=torch.float32)
     angle = position[:, None] * inverse[None, :]
-    tables = _Tables(torch.cos(angle).contiguous().to(device), torch.sin(angle).contiguous().to(device))
+    cos, sin = torch.cos(angle), torch.sin(angle)
+    if stretch != 1.0:
+        cos, sin = cos * stretch, sin * stretch
+    tables = _Tables(cos.contiguous().to(device), sin.contiguous().to(device))
     _TABLES[key] = tables
     return tables
 
 
 class RopeNeox(PositionEncoding):
-    """params: ``head_dim``, ``theta``, ``max_positions``.  No tensors."""
+    """params: ``head_dim``, ``theta``, ``max_positions`` and, optionally, ``rotary_dims`` (only
+    the first that many values of a head turn, value i with value i + rotary_dims/2; default: the
+    whole head) and ``scaling`` (the YaRN constants, see ``yarn_blend``).  No tensors."""
 
     style = ops.ROPE_NEOX
     kernels = ("rope_cache",)
@@ -55,6 +91,10 @@ class RopeNeox(PositionEncoding):
         self.head_dim = int(params["head_dim"])
         self.theta = float(params["theta"])
         self.max_positions = int(params["max_positions"])
+        self.rot_dims = int(params.get("rotary_dims") or self.head_dim)
+        if self.rot_dims % 2 or not 0 < self.rot_dims <= self.head_dim:
+            raise InvalidArgumentError(f"rotary_dims {self.rot_dims} must be even and within the head size {self.head_dim}")
+        self.scaling = dict(params["scaling"]) if params.get("scaling") else None
         self.reach = None   # positions the tables cover; the model's own limit where nobody says
         self._tables = None
 
@@ -74,7 +114,7 @@ class RopeNeox(PositionEncoding):
         if self._tables is None:
             if self.reach is None:
                 self.reach = self.max_positions
-            self._tables = rotary_tables(self.head_dim, self.theta, self.reach, self.device)
+            self._tables = rotary_tables(self.rot_dims, self.theta, self.reach, self.device, self.scaling)
         return self._tables.pair
 
 

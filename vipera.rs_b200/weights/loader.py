@@ -217,8 +217,9 @@ def to_run_dtype(tensor: torch.Tensor, run_dtype: torch.dtype) -> torch.Tensor:
 
 
 def write_model_folder(model_dir: str, config_dict: dict, schema: Schema, seed: int,
-                       dtype: torch.dtype = torch.bfloat16) -> None:
-    """Random-weights mode: write ``config.json`` and ``model.safetensors``."""
+                       dtype: torch.dtype = torch.bfloat16, stored_name=None) -> None:
+    """Random-weights mode: write ``config.json`` and ``model.safetensors``.  ``stored_name`` maps a
+    tensor's name in the schema to the name the file stores it under (default: the same)."""
     os.makedirs(model_dir, exist_ok=True)
     source = RandomSource(schema, seed, dtype)
     with open(os.path.join(model_dir, "config.json"), "w", encoding="utf-8") as handle:
@@ -226,6 +227,6 @@ def write_model_folder(model_dir: str, config_dict: dict, schema: Schema, seed: 
         handle.write("\n")
     write_safetensors(
         os.path.join(model_dir, "model.safetensors"),
-        ((name, source.get(name)) for name in schema),
+        ((stored_name(name) if stored_name else name, source.get(name)) for name in schema),
         metadata={"format": "pt", "seed": seed},
     )
