@@ -81,10 +81,10 @@ def random_tokens(vocab: int, count: int, seed: int) -> List[int]:
 
 
 def run_trace(folder: str, dtype: str, steps: List[dict], max_tokens: int, page_size: int = 64,
-              env_extra=None, timeout: int = 900, max_live: int = 8) -> Dict[int, np.ndarray]:
+              env_extra=None, timeout: int = 900, max_live: int = 8, vocab: int = 0) -> Dict[int, np.ndarray]:
     """Replay ``steps`` with bin/trace_run as a user would (a process of its own) and return
     the logits files it wrote, by step."""
-    vocab = json.load(open(os.path.join(folder, "config.json")))["vocab_size"]
+    vocab = vocab or json.load(open(os.path.join(folder, "config.json")))["vocab_size"]
     out_dir = tempfile.mkdtemp(prefix="vipera_trace_out_")
     text = "".join(json.dumps(step) + "\n" for step in steps)
     env = dict(os.environ)

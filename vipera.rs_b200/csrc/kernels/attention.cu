@@ -16,7 +16,7 @@
 // which adds exp(0 - max) to the softmax's denominator (p_j = e^{s_j} / (1 + sum e^{s_j})).
 //
 // This kernel is the attention of the 32-bit path and takes every head size that is a
-// multiple of 8 up to 256 (keys and values each), any number of heads and groups, any page size.
+// up to 256 (keys and values each; sizes that are not a multiple of 8 are read value by value), any number of heads and groups, any page size.
 #include "common.cuh"
 
 constexpr int kWarpsPerBlock = 4;
@@ -28,6 +28,10 @@ __device__ __forceinline__ float dot_row(const float* __restrict__ q, const T* _
 template <>
 __device__ __forceinline__ float dot_row<float>(const float* __restrict__ q, const float* __restrict__ row, int d) {
   float sum = 0.0f;
+  if (d & 3) {   // rows of such a size do not start on 16 bytes
+    for (int i = 0; i < d; ++i) sum = fmaf(q[i], row[i], sum);
+    return sum;
+  }
   const float4* r4 = reinterpret_cast<const float4*>(row);
   for (int i = 0; i < d / 4; ++i) {
     const float4 v = r4[i];
@@ -42,6 +46,10 @@ __device__ __forceinline__ float dot_row<float>(const float* __restrict__ q, con
 template <>
 __device__ __forceinline__ float dot_row<__nv_bfloat16>(const float* __restrict__ q, const __nv_bfloat16* __restrict__ row, int d) {
   float sum = 0.0f;
+  if (d & 7) {
+    for (int i = 0; i < d; ++i) sum = fmaf(q[i], __bfloat162float(row[i]), sum);
+    return sum;
+  }
   const uint4* r8 = reinterpret_cast<const uint4*>(row);
   for (int i = 0; i < d / 8; ++i) {
     const uint4 raw = r8[i];
@@ -152,8 +160,8 @@ VIPERA_API int vipera_attention(const void* q, void* out, int dtype, const void*
                                 int num_kv_heads, int head_dim, int value_dim, float scale, int window,
                                 int keep_first, int sink, void* stream) {
   if (num_tokens <= 0) return VIPERA_OK;
-  if (head_dim <= 0 || head_dim % 8 != 0 || head_dim > kMaxHeadDim) return VIPERA_BAD_SHAPE;
-  if (value_dim <= 0 || value_dim % 8 != 0 || value_dim > kMaxHeadDim || keep_first < 0) return VIPERA_BAD_SHAPE;
+  if (head_dim <= 0 || head_dim > kMaxHeadDim) return VIPERA_BAD_SHAPE;
+  if (value_dim <= 0 || value_dim > kMaxHeadDim || keep_first < 0) return VIPERA_BAD_SHAPE;
   if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads != 0) return VIPERA_BAD_SHAPE;
   if (page_size <= 0 || table_width <= 0 || window < 0) return VIPERA_BAD_ARGUMENT;
   cudaStream_t s = static_cast<cudaStream_t>(stream);

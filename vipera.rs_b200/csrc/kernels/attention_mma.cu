@@ -31,7 +31,12 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
                          const __nv_bfloat16* __restrict__ k_pool, const __nv_bfloat16* __restrict__ v_pool,
                          const int* __restrict__ entry_starts, const int* __restrict__ entry_pos0,
                          const int* __restrict__ block_table, int table_width, int page_size, int num_entries,
-                         int num_heads, int num_kv_heads, float scale, int window, int skip_single) {
+                         int num_heads, int num_kv_heads, float scale, int window, int skip_single,
+                         int keep_first, int sink) {
+  // keep_first: with a window, keys 0 .. keep_first-1 stay visible to every later query.  The
+  // block folds them first, as tiles of their own with a mask of their own (keys below both
+  // keep_first and the row's window), then the window's tiles as ever.  sink != 0: a key of
+  // score 0 without a value joins every row's softmax, which adds exp(-max) to its sum.
   constexpr int kQ = 64, kKeys = 64, kThreads = 128 * HPC;
   extern __shared__ __align__(128) uint8_t smem[];
   pdl_launch_dependents();
@@ -78,14 +83,19 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
   const int first_key = window > 0 ? max(0, pos0 - window + 1) : 0;
   const int first_block = first_key / kKeys;
   const int end_key = last_pos + 1;
-  const int num_blocks = (end_key + kKeys - 1) / kKeys - first_block;
+  // kept keys some row of the tile sees outside its window: those below the last row's window
+  const int kept_end = (window > 0 && keep_first > 0) ? min(keep_first, max(0, last_pos - window + 1)) : 0;
+  const int kept_blocks = (kept_end + kKeys - 1) / kKeys;
+  const int num_blocks = kept_blocks + (end_key + kKeys - 1) / kKeys - first_block;
 
   auto load_block = [&](int block, int buffer) {
-    const int key0 = (first_block + block) * kKeys;
+    const bool kept = block < kept_blocks;
+    const int key0 = kept ? block * kKeys : (first_block + block - kept_blocks) * kKeys;
+    const int from = kept ? 0 : first_key, to = kept ? kept_end : end_key;
     load_kv_tile<D, kKeys, kThreads>(k_tiles + buffer * kKeys * D * 2, k_pool, table, page_size, num_kv_heads, kv_head,
-                                     key0, first_key, end_key, threadIdx.x);
+                                     key0, from, to, threadIdx.x);
     load_kv_tile<D, kKeys, kThreads>(v_tiles + buffer * kKeys * D * 2, v_pool, table, page_size, num_kv_heads, kv_head,
-                                     key0, first_key, end_key, threadIdx.x);
+                                     key0, from, to, threadIdx.x);
   };
   load_block(0, 0);
   cp_async_commit();
@@ -97,13 +107,14 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[n][i] = 0.0f;
   float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.0f, 0.0f};
-  int row_first[2], row_limit[2];
+  int row_first[2], row_limit[2], kept_first[2] = {0, 0}, kept_limit[2];
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     const int row = q_warp * 16 + (lane >> 2) + r * 8;
     const int position = pos0 + row;
     row_limit[r] = row < tokens_here ? position : -1;  // rows past the end see nothing
     row_first[r] = window > 0 ? max(0, position - window + 1) : 0;
+    kept_limit[r] = row < tokens_here ? min(keep_first, row_first[r]) - 1 : -1;   // kept keys the window does not hold
   }
   const float scale_log2 = scale * kLog2e;
 
@@ -119,9 +130,13 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
         ldmatrix_x4(q_frag[ks], q_tiles + (warp >> 2) * kQ * D * 2 +
                                     tile_offset<D>(q_warp * 16 + (lane & 15), ks * 2 + (lane >> 4)));
     }
-    const int key0 = (first_block + block) * kKeys;
+    const bool kept = block < kept_blocks;
+    const int key0 = kept ? block * kKeys : (first_block + block - kept_blocks) * kKeys;
     // a warp whose 16 queries all stand before this block has nothing to see in it
-    if (key0 <= pos0 + q_warp * 16 + 15)
+    if (kept)
+      fold_block<D, kKeys>(q_frag, k_tiles + buffer * kKeys * D * 2, v_tiles + buffer * kKeys * D * 2, key0,
+                           kept_first, kept_limit, scale_log2, row_max, row_sum, acc);
+    else if (key0 <= pos0 + q_warp * 16 + 15)
       fold_block<D, kKeys>(q_frag, k_tiles + buffer * kKeys * D * 2, v_tiles + buffer * kKeys * D * 2, key0,
                            row_first, row_limit, scale_log2, row_max, row_sum, acc);
     __syncthreads();
@@ -136,6 +151,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
     sum += __shfl_xor_sync(0xffffffffu, sum, 2);
     const int row = q_warp * 16 + (lane >> 2) + r * 8;
     if (row >= tokens_here) continue;
+    if (sink) sum += exp2f(-row_max[r]);   // the sink's score is 0; the maximum is in units of log2
     const float inverse = 1.0f / sum;
     __nv_bfloat16* dst = out + (static_cast<size_t>(token0 + row) * num_heads + head) * D;
 #pragma unroll
@@ -595,7 +611,7 @@ template <int D, int HPC>
 int launch_prefill_variant(const void* q, void* out, const void* k_pool, const void* v_pool, const int* entry_starts,
                            const int* entry_pos0, const int* block_table, int table_width, int page_size,
                            int num_entries, int num_tokens, int num_heads, int num_kv_heads, float scale, int window,
-                           int skip_single, cudaStream_t s) {
+                           int skip_single, int keep_first, int sink, cudaStream_t s) {
   constexpr int kSmem = (HPC * 64 + 4 * 64) * D * 2;
   static bool configured = false;
   if (!configured) {
@@ -608,22 +624,22 @@ int launch_prefill_variant(const void* q, void* out, const void* k_pool, const v
   return vipera_launch(attention_prefill_kernel<D, HPC>, grid, dim3(128 * HPC), kSmem, s,
       static_cast<const __nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(k_pool),
       static_cast<const __nv_bfloat16*>(v_pool), entry_starts, entry_pos0, block_table, table_width, page_size,
-      num_entries, num_heads, num_kv_heads, scale, window, skip_single);
+      num_entries, num_heads, num_kv_heads, scale, window, skip_single, keep_first, sink);
 }
 
 template <int D>
 int launch_prefill(const void* q, void* out, const void* k_pool, const void* v_pool, const int* entry_starts,
                    const int* entry_pos0, const int* block_table, int table_width, int page_size, int num_entries,
                    int num_tokens, int num_heads, int num_kv_heads, float scale, int window, int skip_single,
-                   cudaStream_t s) {
+                   int keep_first, int sink, cudaStream_t s) {
   // two heads per block where the heads of a KV group pair up
   if ((num_heads / num_kv_heads) % 2 == 0)
     return launch_prefill_variant<D, 2>(q, out, k_pool, v_pool, entry_starts, entry_pos0, block_table, table_width,
                                         page_size, num_entries, num_tokens, num_heads, num_kv_heads, scale, window,
-                                        skip_single, s);
+                                        skip_single, keep_first, sink, s);
   return launch_prefill_variant<D, 1>(q, out, k_pool, v_pool, entry_starts, entry_pos0, block_table, table_width,
                                       page_size, num_entries, num_tokens, num_heads, num_kv_heads, scale, window,
-                                      skip_single, s);
+                                      skip_single, keep_first, sink, s);
 }
 
 // The one-kernel form serves a step of few entries whose groups of heads fit one MMA tile.
@@ -740,21 +756,42 @@ int launch_decode(const void* q, void* out, const void* k_pool, const void* v_po
 // entry_starts [entries + 1] are cumulative token counts and entry_pos0 [entries] the position
 // of each entry's first token.  Head sizes: 64 and 128.  With `skip_single`, entries of one
 // token are left out (the caller runs vipera_attention_decode over them).
+static int run_prefill(const void* q, void* out, const void* k_pool, const void* v_pool, const int* entry_starts,
+                       const int* entry_pos0, const int* block_table, int table_width, int page_size, int num_entries,
+                       int num_tokens, int num_heads, int num_kv_heads, int head_dim, float scale, int window,
+                       int skip_single, int keep_first, int sink, void* stream) {
+  if (num_tokens <= 0 || num_entries <= 0) return VIPERA_OK;
+  if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads || keep_first < 0) return VIPERA_BAD_SHAPE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (head_dim == 128)
+    return launch_prefill<128>(q, out, k_pool, v_pool, entry_starts, entry_pos0, block_table, table_width, page_size,
+                               num_entries, num_tokens, num_heads, num_kv_heads, scale, window, skip_single, keep_first,
+                               sink, s);
+  if (head_dim == 64)
+    return launch_prefill<64>(q, out, k_pool, v_pool, entry_starts, entry_pos0, block_table, table_width, page_size,
+                              num_entries, num_tokens, num_heads, num_kv_heads, scale, window, skip_single, keep_first,
+                              sink, s);
+  return VIPERA_BAD_SHAPE;
+}
+
 VIPERA_API int vipera_attention_prefill(const void* q, void* out, const void* k_pool, const void* v_pool,
                                         const int* entry_starts, const int* entry_pos0, const int* block_table,
                                         int table_width, int page_size, int num_entries, int num_tokens,
                                         int num_heads, int num_kv_heads, int head_dim, float scale, int window,
                                         int skip_single, void* stream) {
-  if (num_tokens <= 0 || num_entries <= 0) return VIPERA_OK;
-  if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads) return VIPERA_BAD_SHAPE;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (head_dim == 128)
-    return launch_prefill<128>(q, out, k_pool, v_pool, entry_starts, entry_pos0, block_table, table_width, page_size,
-                               num_entries, num_tokens, num_heads, num_kv_heads, scale, window, skip_single, s);
-  if (head_dim == 64)
-    return launch_prefill<64>(q, out, k_pool, v_pool, entry_starts, entry_pos0, block_table, table_width, page_size,
-                              num_entries, num_tokens, num_heads, num_kv_heads, scale, window, skip_single, s);
-  return VIPERA_BAD_SHAPE;
+  return run_prefill(q, out, k_pool, v_pool, entry_starts, entry_pos0, block_table, table_width, page_size, num_entries,
+                     num_tokens, num_heads, num_kv_heads, head_dim, scale, window, skip_single, 0, 0, stream);
+}
+
+// The same with kept first keys (`keep_first`, counts with a window only) and a sink (`sink` != 0).
+VIPERA_API int vipera_attention_prefill_kept(const void* q, void* out, const void* k_pool, const void* v_pool,
+                                             const int* entry_starts, const int* entry_pos0, const int* block_table,
+                                             int table_width, int page_size, int num_entries, int num_tokens,
+                                             int num_heads, int num_kv_heads, int head_dim, float scale, int window,
+                                             int skip_single, int keep_first, int sink, void* stream) {
+  return run_prefill(q, out, k_pool, v_pool, entry_starts, entry_pos0, block_table, table_width, page_size, num_entries,
+                     num_tokens, num_heads, num_kv_heads, head_dim, scale, window, skip_single,
+                     window > 0 ? keep_first : 0, sink, stream);
 }
 
 // Floats of scratch a decode launch needs: (2 + d) per (entry, head, slice).

@@ -72,7 +72,8 @@ struct GemmParams {
   int tiles_x, tiles_y, splits, k_blocks_per_split;
   int epilogue;
   int out_dtype;
-  const float* bias;
+  const float* bias;  // [N] or null; counts in every ending (in the gated unit: interleaved like the rows)
+  int activation;     // of the gated unit: ACT_SILU or ACT_GELU_TANH
   void* out;
   float* resid;
   int tma_ending;    // 1: the ending goes through shared memory and TMA stores (map_out)
@@ -278,6 +279,11 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 // up * silu(gate); the quotient with the hardware's reciprocal (the result is rounded to
 // bfloat16 by every caller on the tensor-core path, which hides the last bits)
 __device__ __forceinline__ float silu_mul(float gate, float up) { return up * __fdividef(gate, 1.0f + __expf(-gate)); }
+// The gated unit: up * act(gate).
+__device__ __forceinline__ float glu_mul(float gate, float up, int activation) {
+  if (activation == ACT_GELU_TANH) return up * gate_activation(gate, ACT_GELU_TANH);
+  return silu_mul(gate, up);
+}
 
 #ifndef VIPERA_SMALL_BUDGET
 #define VIPERA_SMALL_BUDGET 100
@@ -321,7 +327,8 @@ __device__ __forceinline__ void finish_chunk(const GemmParams& p, const float* v
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
         if (col0 + 16 + i >= N) break;
-        const float value = silu_mul(v[i], v[16 + i]);
+        const float value = glu_mul(v[i] + (p.bias ? p.bias[col0 + i] : 0.0f),
+                                    v[16 + i] + (p.bias ? p.bias[col0 + 16 + i] : 0.0f), p.activation);
         if (p.out_dtype == VIPERA_BF16) dst[i] = __float2bfloat16_rn(value); else dst32[i] = value;
       }
       return;
@@ -333,7 +340,7 @@ __device__ __forceinline__ void finish_chunk(const GemmParams& p, const float* v
       if (n >= N) break;
       const size_t at = static_cast<size_t>(t) * N + n;
       if (p.epilogue == EPI_RESIDUAL) {
-        p.resid[at] += v[i];
+        p.resid[at] += v[i] + (p.bias ? p.bias[n] : 0.0f);
       } else {
         const float value = v[i] + (p.bias ? p.bias[n] : 0.0f);
         if (p.out_dtype == VIPERA_BF16) static_cast<__nv_bfloat16*>(p.out)[at] = __float2bfloat16_rn(value);
@@ -347,13 +354,15 @@ __device__ __forceinline__ void finish_chunk(const GemmParams& p, const float* v
       // lanes 0-15 of a warp hold gate rows, lanes 16-31 the up rows of the same features
       const int inter = N >> 1;
       const int f = ((n - lane) >> 1) + (lane & 15);
+      const float own_bias = (p.bias && n < N) ? p.bias[n] : 0.0f;
+      const float other_bias = __shfl_xor_sync(0xffffffffu, own_bias, 16);
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
         if (i >= width) break;
         const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
         const int t = col0 + i;
         if (lane < 16 && t < p.tokens && n + 16 < N) {
-          const float value = silu_mul(v[i], other);
+          const float value = glu_mul(v[i] + own_bias, other + other_bias, p.activation);
           const size_t at = static_cast<size_t>(t) * inter + f;
           if (p.out_dtype == VIPERA_BF16) static_cast<__nv_bfloat16*>(p.out)[at] = __float2bfloat16_rn(value);
           else static_cast<float*>(p.out)[at] = value;
@@ -362,7 +371,7 @@ __device__ __forceinline__ void finish_chunk(const GemmParams& p, const float* v
       return;
     }
     if (n >= N) return;
-    const float bias = (p.epilogue == EPI_STORE && p.bias) ? p.bias[n] : 0.0f;
+    const float bias = p.bias ? p.bias[n] : 0.0f;
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
       if (i >= width) break;
@@ -370,7 +379,7 @@ __device__ __forceinline__ void finish_chunk(const GemmParams& p, const float* v
       if (t >= p.tokens) break;
       const size_t at = static_cast<size_t>(t) * N + n;
       if (p.epilogue == EPI_RESIDUAL) {
-        p.resid[at] += v[i];
+        p.resid[at] += v[i] + bias;
       } else {
         const float value = v[i] + bias;
         if (p.out_dtype == VIPERA_BF16) static_cast<__nv_bfloat16*>(p.out)[at] = __float2bfloat16_rn(value);
@@ -812,10 +821,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
               for (int q4 = 0; q4 < 4; ++q4) {
                 float v[32];
                 tmem_load_32(taddr + c + q4 * 32, v);
+                if (p.bias) {
+#pragma unroll
+                  for (int i = 0; i < 32; ++i) {
+                    const int n = ty * BN + c + q4 * 32 + i;
+                    v[i] += n < p.features ? p.bias[n] : 0.0f;
+                  }
+                }
                 uint32_t packed[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i)
-                  packed[i] = pack_bf16x2(silu_mul(v[2 * i], v[16 + 2 * i]), silu_mul(v[2 * i + 1], v[16 + 2 * i + 1]));
+                  packed[i] = pack_bf16x2(glu_mul(v[2 * i], v[16 + 2 * i], p.activation),
+                                          glu_mul(v[2 * i + 1], v[16 + 2 * i + 1], p.activation));
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                   const int chunk = (q4 * 2 + h) ^ (lane & 7);
@@ -846,7 +863,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 #pragma unroll
                 for (int i = 0; i < 32; ++i) v[i] += more[i];
               }
-              if (p.epilogue == EPI_STORE && p.bias) {
+              if (p.bias) {
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
                   const int n = ty * BN + c + i;
@@ -980,7 +997,8 @@ splitk_finish_kernel(const GemmParams p) {
     return sum;
   };
   if (swiglu) {
-    const float value = silu_mul(total(n0), total(n1));
+    const float value = glu_mul(total(n0) + (p.bias ? p.bias[n0] : 0.0f), total(n1) + (p.bias ? p.bias[n1] : 0.0f),
+                                p.activation);
     const size_t at = static_cast<size_t>(t) * width + o;
     if (p.out_dtype == VIPERA_BF16) static_cast<__nv_bfloat16*>(p.out)[at] = __float2bfloat16_rn(value);
     else static_cast<float*>(p.out)[at] = value;
@@ -989,7 +1007,7 @@ splitk_finish_kernel(const GemmParams p) {
   const float value = total(n0);
   const size_t at = static_cast<size_t>(t) * N + o;
   if (p.epilogue == EPI_RESIDUAL) {
-    atomicAdd(p.resid + at, value);   // one addition per element: no need to read the old value back
+    atomicAdd(p.resid + at, value + (p.bias ? p.bias[o] : 0.0f));   // one addition per element: no need to read the old value back
   } else {
     const float biased = value + (p.bias ? p.bias[o] : 0.0f);
     if (p.out_dtype == VIPERA_BF16) static_cast<__nv_bfloat16*>(p.out)[at] = __float2bfloat16_rn(biased);
@@ -1035,10 +1053,20 @@ splitk_finish4_kernel(const GemmParams p) {
   float4 value = total(n0);
   const size_t at = static_cast<size_t>(t) * width + o;
   if (swiglu) {
-    const float4 up = total(n0 + 16);
-    value = make_float4(silu_mul(value.x, up.x), silu_mul(value.y, up.y), silu_mul(value.z, up.z), silu_mul(value.w, up.w));
+    float4 up = total(n0 + 16);
+    if (p.bias) {
+      const float4 bg = *reinterpret_cast<const float4*>(p.bias + n0), bu = *reinterpret_cast<const float4*>(p.bias + n0 + 16);
+      value = make_float4(value.x + bg.x, value.y + bg.y, value.z + bg.z, value.w + bg.w);
+      up = make_float4(up.x + bu.x, up.y + bu.y, up.z + bu.z, up.w + bu.w);
+    }
+    value = make_float4(glu_mul(value.x, up.x, p.activation), glu_mul(value.y, up.y, p.activation),
+                        glu_mul(value.z, up.z, p.activation), glu_mul(value.w, up.w, p.activation));
   } else if (p.epilogue == EPI_RESIDUAL) {
     // one addition per element, nothing read back
+    if (p.bias) {
+      const float4 b = *reinterpret_cast<const float4*>(p.bias + o);
+      value = make_float4(value.x + b.x, value.y + b.y, value.z + b.z, value.w + b.w);
+    }
     float* dst = p.resid + at;
     atomicAdd(dst, value.x);
     atomicAdd(dst + 1, value.y);
@@ -1524,7 +1552,7 @@ static int launch_pairs(const CUtensorMap& map_x, const CUtensorMap& map_y, cons
 // `rope`: for EPI_ROPE_CACHE, the fields of that ending (the others are filled in here).
 static int run_gemm(const void* A, const void* W, int T, int N, int K, int epilogue, const float* bias, void* out,
                     int out_dtype, float* resid, float* scratch, size_t scratch_bytes, int* status, void* stream,
-                    const GemmParams* rope) {
+                    const GemmParams* rope, int activation = ACT_SILU) {
   if (T <= 0) return VIPERA_OK;
   if (N <= 0 || K <= 0 || (K % 8) != 0) return VIPERA_BAD_SHAPE;
   if (epilogue == EPI_SWIGLU && (N % 32) != 0) return VIPERA_BAD_SHAPE;
@@ -1563,6 +1591,7 @@ static int run_gemm(const void* A, const void* W, int T, int N, int K, int epilo
   p.epilogue = epilogue;
   p.out_dtype = out_dtype;
   p.bias = bias;
+  p.activation = activation;
   p.out = out;
   p.resid = resid;
   p.scratch = scratch;
@@ -1603,7 +1632,8 @@ static int run_gemm(const void* A, const void* W, int T, int N, int K, int epilo
     // The device refused the clusters (nothing has run): from now on blocks alone, this product too.
     cudaGetLastError();
     pair_mode() = 0;
-    return run_gemm(A, W, T, N, K, epilogue, bias, out, out_dtype, resid, scratch, scratch_bytes, status, stream, rope);
+    return run_gemm(A, W, T, N, K, epilogue, bias, out, out_dtype, resid, scratch, scratch_bytes, status, stream, rope,
+                    activation);
   }
   if (plan.even_shares) {
     if (plan.bn == 256) return launch_variant<256, false, true>(map_x, map_y, map_out, p, grid, s);
@@ -1627,7 +1657,20 @@ VIPERA_API int vipera_gemm_tc(const void* A, const void* W, int T, int N, int K,
                               void* out, int out_dtype, float* resid, float* scratch, size_t scratch_bytes,
                               int* status, void* stream) {
   if (epilogue == EPI_ROPE_CACHE) return VIPERA_BAD_ARGUMENT;  // that ending has an entry point of its own
-  return run_gemm(A, W, T, N, K, epilogue, bias, out, out_dtype, resid, scratch, scratch_bytes, status, stream, nullptr);
+  // the form the earlier callers know: a bias with the plain store only, silu in the gated unit
+  return run_gemm(A, W, T, N, K, epilogue, epilogue == EPI_STORE ? bias : nullptr, out, out_dtype, resid, scratch,
+                  scratch_bytes, status, stream, nullptr);
+}
+
+// The same with a bias in every ending (for the gated unit it is interleaved like the rows) and the
+// gated unit's activation chosen.
+VIPERA_API int vipera_gemm_tc_act(const void* A, const void* W, int T, int N, int K, int epilogue, const float* bias,
+                                  void* out, int out_dtype, float* resid, int activation, float* scratch,
+                                  size_t scratch_bytes, int* status, void* stream) {
+  if (epilogue == EPI_ROPE_CACHE) return VIPERA_BAD_ARGUMENT;
+  if (activation != ACT_SILU && activation != ACT_GELU_TANH) return VIPERA_BAD_ARGUMENT;
+  return run_gemm(A, W, T, N, K, epilogue, bias, out, out_dtype, resid, scratch, scratch_bytes, status, stream, nullptr,
+                  activation);
 }
 
 // What the q/k/v ending needs beside the product itself (mirrored by the caller).

@@ -53,6 +53,7 @@ struct GemvParams {
   const int* token_entry;
   const int* block_table;
   int table_width, page_size, write_cache;
+  int activation;               // of the gated unit: ACT_SILU or ACT_GELU_TANH
 };
 
 constexpr int kGemvMaxShared = 200 * 1024;
@@ -102,9 +103,9 @@ __device__ __forceinline__ Ending prepare_ending(const GemvParams& p, int row_lo
   e.active = 1;
   e.rotate = 0;
   const bool has_hi = row_hi < p.N;
-  if (p.epilogue == GEMV_STORE) {
-    if (p.bias) { e.bias_lo = p.bias[row_lo]; if (has_hi) e.bias_hi = p.bias[row_hi]; }
-  } else if (p.epilogue == GEMV_ROPE_CACHE) {
+  if (p.epilogue != GEMV_ROPE_CACHE) {
+    if (p.bias) { if (row_lo < p.N) e.bias_lo = p.bias[row_lo]; if (has_hi) e.bias_hi = p.bias[row_hi]; }
+  } else {
     if (p.bias) { e.bias_lo = p.bias[row_lo]; e.bias_hi = p.bias[row_hi]; }
     const int d = p.head_dim, half = d >> 1;
     const int head = row_lo / d, i = row_lo % d;
@@ -140,11 +141,14 @@ __device__ __forceinline__ void finish(const GemvParams& p, const Ending& e, int
   if (p.epilogue == GEMV_RESIDUAL) {
     // every element of the stream gets one addition from one thread: an addition that does not
     // read the old value back gives the same sum and spares the ending a memory round trip
-    atomicAdd(p.resid + static_cast<size_t>(t) * p.N + row_lo, v_lo);
-    if (has_hi) atomicAdd(p.resid + static_cast<size_t>(t) * p.N + row_hi, v_hi);
+    atomicAdd(p.resid + static_cast<size_t>(t) * p.N + row_lo, v_lo + e.bias_lo);
+    if (has_hi) atomicAdd(p.resid + static_cast<size_t>(t) * p.N + row_hi, v_hi + e.bias_hi);
   } else if (p.epilogue == GEMV_SWIGLU) {
     const int feature = (row_lo >> 5) * 16 + (row_lo & 15);
-    const float value = v_hi * (v_lo / (1.0f + __expf(-v_lo)));
+    v_lo += e.bias_lo;
+    v_hi += e.bias_hi;
+    const float value = p.activation == ACT_GELU_TANH ? v_hi * gate_activation(v_lo, ACT_GELU_TANH)
+                                                      : v_hi * (v_lo / (1.0f + __expf(-v_lo)));
     const size_t at = static_cast<size_t>(t) * (p.N >> 1) + feature;
     if (p.out_dtype == VIPERA_BF16) static_cast<__nv_bfloat16*>(p.out)[at] = __float2bfloat16_rn(value);
     else static_cast<float*>(p.out)[at] = value;

@@ -354,8 +354,8 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: 
     count = q.shape[0]
     value_dim = head_dim if value_dim is None else int(value_dim)
     for size in (head_dim, value_dim):
-        if size % 8 or size > 256:
-            raise UnsupportedError(f"attention: head size {size} is not a multiple of 8 up to 256")
+        if not 0 < size <= 256:
+            raise UnsupportedError(f"attention: head size {size} is not within 1 to 256")
     if q.shape[1] != num_heads * head_dim or tuple(out.shape) != (count, num_heads * value_dim) or out.dtype != q.dtype:
         raise InvalidArgumentError("attention: q must be [tokens, heads * d] and out [tokens, heads * value size], of one dtype")
     if k_pool.dtype != q.dtype or v_pool.dtype != q.dtype or v_pool.shape[:3] != k_pool.shape[:3]:
@@ -540,10 +540,12 @@ def gemm_tc_pairs(mode: int) -> int:
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_STORE,
             bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-            resid: Optional[torch.Tensor] = None) -> None:
-    """a[M, K] times w[N, K] transposed in bfloat16 on the tensor cores (tcgen05, TMA)."""
-    fn = _function("gemm_tc", "vipera_gemm_tc",
-                   [_c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void, _c_int, _c_void, _c_void,
+            resid: Optional[torch.Tensor] = None, activation: int = ACT_SILU) -> None:
+    """a[M, K] times w[N, K] transposed in bfloat16 on the tensor cores (tcgen05, TMA).  ``bias``
+    counts in every ending (for the gated unit it is interleaved like the rows); ``activation``
+    is the gated unit's."""
+    fn = _function("gemm_tc", "vipera_gemm_tc_act",
+                   [_c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void, _c_int, _c_void, _c_int, _c_void,
                     ctypes.c_size_t, _c_void, _c_void])
     m, k = a.shape
     n = w.shape[0]
@@ -558,7 +560,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_STORE,
     _check(fn(_gpu(a, "a", torch.bfloat16), _gpu(w, "w", torch.bfloat16), m, n, k, epilogue,
               _opt(bias, "bias", torch.float32), _opt(out, "out"),
               dtype_code(out.dtype) if out is not None else F32, _opt(resid, "resid", torch.float32),
-              None if scratch is None else scratch.data_ptr(),
+              int(activation), None if scratch is None else scratch.data_ptr(),
               0 if scratch is None else scratch.numel() * 4,
               state["status"].data_ptr(), _stream()), "gemm_tc",
            kernels=2 if scratch_bytes and gemm_tc_plan(m, n, k, epilogue, _even_ok(n, epilogue, out))["splits"] > 1 else 1)
@@ -658,11 +660,13 @@ TC_ATTENTION_HEAD_DIMS = (64, 128)
 def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, *,
                       entry_starts: torch.Tensor, entry_pos0: torch.Tensor, block_table: torch.Tensor,
                       num_entries: int, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
-                      window: int = 0, skip_single: bool = False) -> None:
+                      window: int = 0, skip_single: bool = False, keep_first: int = 0, sink: bool = False) -> None:
     """Flash-style attention of a step whose entries bring any number of tokens (bfloat16,
     head sizes 64 and 128), on tcgen05 with accumulators in tensor memory
     (VIPERA_ATTENTION_TC=0 keeps it on the mma.sync kernel).
-    ``skip_single`` leaves entries of one token out: attention_decode with ``entry_starts`` runs them."""
+    ``skip_single`` leaves entries of one token out: attention_decode with ``entry_starts`` runs them.
+    ``keep_first`` (with a window: that many first keys stay visible) and ``sink`` (one added to the
+    softmax's denominator) are served by the mma.sync kernel."""
     if head_dim not in MMA_HEAD_DIMS:
         raise UnsupportedError(f"attention_prefill: head size {head_dim} (built: 64, 128)")
     count = q.shape[0]
@@ -677,6 +681,11 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, 
              float(scale), int(window or 0))
     kinds = [_c_void] * 7 + [_c_int] * 7 + [_c_float, _c_int]
     skip = 1 if skip_single else 0
+    keep_first = int(keep_first or 0) if window else 0
+    if keep_first or sink:
+        fn = _function("attention_mma", "vipera_attention_prefill_kept", kinds + [_c_int, _c_int, _c_int, _c_void])
+        _check(fn(*pointers, *sizes, skip, keep_first, 1 if sink else 0, _stream()), "attention_prefill")
+        return
     if head_dim in TC_ATTENTION_HEAD_DIMS and os.environ.get("VIPERA_ATTENTION_TC", "1") != "0":
         fn = _function("attention_tc", "vipera_attention_prefill_tc", kinds + [_c_int, _c_int, _c_void, _c_void])
         _check(fn(*pointers, *sizes, k_pool.shape[0], skip, kernel_status_word(q.device).data_ptr(), _stream()),
@@ -802,7 +811,7 @@ class _GemvParams(ctypes.Structure):
         ("num_heads", _c_int), ("num_kv_heads", _c_int), ("head_dim", _c_int), ("rope_style", _c_int),
         ("positions", _c_void), ("cos_table", _c_void), ("sin_table", _c_void), ("q_out", _c_void),
         ("k_pool", _c_void), ("v_pool", _c_void), ("token_entry", _c_void), ("block_table", _c_void),
-        ("table_width", _c_int), ("page_size", _c_int), ("write_cache", _c_int),
+        ("table_width", _c_int), ("page_size", _c_int), ("write_cache", _c_int), ("activation", _c_int),
     ]
 
 
@@ -812,7 +821,8 @@ _gemv_checked = False
 def gemv_small(w: torch.Tensor, *, a: Optional[torch.Tensor] = None, x: Optional[torch.Tensor] = None,
                norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0, rows: Optional[torch.Tensor] = None,
                tokens: Optional[int] = None, epilogue: int = GEMV_STORE, bias: Optional[torch.Tensor] = None,
-               out: Optional[torch.Tensor] = None, resid: Optional[torch.Tensor] = None, rope: Optional[dict] = None) -> None:
+               out: Optional[torch.Tensor] = None, resid: Optional[torch.Tensor] = None, rope: Optional[dict] = None,
+               activation: int = ACT_SILU) -> None:
     """w[N, K] (bfloat16) times at most 32 tokens.  The input is either ``a`` (bfloat16 [T, K])
     or the float32 residual stream ``x`` with an RMSNorm (``norm_weight``, ``eps``, optional
     ``rows`` choosing which rows of x are the tokens) computed on the way.  ``rope`` holds
@@ -861,7 +871,8 @@ def gemv_small(w: torch.Tensor, *, a: Optional[torch.Tensor] = None, x: Optional
             p.table_width, p.page_size = r["block_table"].shape[1], r["page_size"]
     else:
         _check_gemm_outputs(t, n, epilogue, bias, out, resid)
-        p.bias = _opt(bias, "bias", torch.float32) if epilogue == GEMV_STORE else None
+        p.bias = _opt(bias, "bias", torch.float32)
+        p.activation = int(activation)
         p.out = _opt(out, "out")
         p.out_dtype = dtype_code(out.dtype) if out is not None else F32
         p.resid = _opt(resid, "resid", torch.float32)

@@ -70,8 +70,8 @@ class GQAttention(Mixer):
         self.sink = bool(params.get("sink", False))
         self.scale = float(params["softmax_scale"])
         for size in (self.head_dim, self.value_dim):
-            if size % 8 or size > 256:
-                raise UnsupportedError(f"head size {size}: the attention kernels take multiples of 8 up to 256")
+            if not 0 < size <= 256:
+                raise UnsupportedError(f"head size {size}: the attention kernels take sizes up to 256")
         if self.num_heads % self.num_kv_heads:
             raise UnsupportedError("the number of heads must be a multiple of the number of KV heads")
         qn, kn, vn, on = self._names(params)
@@ -93,7 +93,7 @@ class GQAttention(Mixer):
         # the tensor-core attention kernels serve bfloat16 with head sizes 64 and 128; everything
         # else runs through the general kernel
         own = ["rope_cache", "attention"]
-        if self.dtype == torch.bfloat16 and self.head_dim in (64, 128) and self.common_form:
+        if self.dtype == torch.bfloat16 and self.head_dim in (64, 128) and self.value_dim == self.head_dim:
             own.append("attention_mma")
             if self.head_dim in ops.TC_ATTENTION_HEAD_DIMS:
                 own.append("attention_tc")
@@ -107,9 +107,11 @@ class GQAttention(Mixer):
 
     @classmethod
     def cache_request_for(cls, params):
-        return PagedKV(int(params["num_kv_heads"]), int(params["head_dim"]), params.get("window"),
-                       value_dim=int(params.get("value_dim") or params["head_dim"]),
-                       keep_first=int(params.get("keep_first") or 0))
+        value_dim = int(params.get("value_dim") or params["head_dim"])
+        window = params.get("window")
+        return PagedKV(int(params["num_kv_heads"]), int(params["head_dim"]), window,
+                       value_dim=value_dim if value_dim != int(params["head_dim"]) else None,
+                       keep_first=int(params.get("keep_first") or 0) if window else 0)
 
     @classmethod
     def workspace_bytes(cls, params, tokens, element_bytes):
@@ -181,7 +183,18 @@ class GQAttention(Mixer):
         kernel otherwise; in every other case the general kernel."""
         heads, kv_heads, d = self.num_heads, self.num_kv_heads, self.head_dim
         window = self.window or 0
-        if ctx.dtype == torch.bfloat16 and d in ops.MMA_HEAD_DIMS and self.common_form:
+        if (ctx.dtype == torch.bfloat16 and d in ops.MMA_HEAD_DIMS and self.value_dim == d
+                and (self.keep_first or self.sink) and not ctx.all_single):
+            # kept first keys and the sink are known to the mma.sync flash kernel, which then takes
+            # every entry of the step, those of one token too; steps of single tokens only take
+            # the general kernel below
+            ops.attention_prefill(q, mixed, cache.k, cache.v, entry_starts=ctx.entry_starts,
+                                  entry_pos0=ctx.entry_pos0, block_table=table, num_entries=ctx.num_entries,
+                                  num_heads=heads, num_kv_heads=kv_heads, head_dim=d, scale=self.scale,
+                                  window=window, keep_first=self.keep_first, sink=self.sink)
+            return
+        if (ctx.dtype == torch.bfloat16 and d in ops.MMA_HEAD_DIMS and self.value_dim == d
+                and not self.keep_first and not self.sink):
             if ctx.all_single:
                 chunk, splits = ops.decode_splits(ctx.num_entries, kv_heads, max(ctx.max_kv_len, 1),
                                                   ops.sm_count(q.device))

@@ -108,22 +108,18 @@ class Linear:
         bias = self.bias
         lazy = a if isinstance(a, NormedInput) else None
         tokens = lazy.num_rows if lazy is not None else a.shape[0]
-        if (bias is not None and epilogue != ops.EPI_STORE) or activation != ops.ACT_SILU:
-            # the tensor-core kernels' endings know a bias with a plain store and silu only
-            ops.gemm_simt(lazy.tensor() if lazy is not None else a, self.weight, epilogue=epilogue, bias=bias,
-                          out=out, resid=resid, activation=activation)
-            return
         if self.takes_small(tokens):
             if lazy is not None and lazy.fusable and lazy._tensor is None:
                 ops.gemv_small(self.weight, x=lazy.residual, norm_weight=lazy.norm.weight, eps=lazy.norm.eps,
-                               rows=lazy.rows, tokens=tokens, epilogue=epilogue, bias=bias, out=out, resid=resid)
+                               rows=lazy.rows, tokens=tokens, epilogue=epilogue, bias=bias, out=out, resid=resid,
+                               activation=activation)
             else:
                 ops.gemv_small(self.weight, a=lazy.tensor() if lazy is not None else a, epilogue=epilogue,
-                               bias=bias, out=out, resid=resid)
+                               bias=bias, out=out, resid=resid, activation=activation)
             return
         if lazy is not None:
             a = lazy.tensor()
         if self.tensor_core and a.dtype == torch.bfloat16 and a.is_contiguous() and a.data_ptr() % 16 == 0:
-            ops.gemm_tc(a, self.weight, epilogue=epilogue, bias=bias, out=out, resid=resid)
+            ops.gemm_tc(a, self.weight, epilogue=epilogue, bias=bias, out=out, resid=resid, activation=activation)
             return
-        ops.gemm_simt(a, self.weight, epilogue=epilogue, bias=bias, out=out, resid=resid)
+        ops.gemm_simt(a, self.weight, epilogue=epilogue, bias=bias, out=out, resid=resid, activation=activation)

@@ -15,7 +15,7 @@ from ..errors import UnsupportedError
 from ..kernels import ops
 from ..weights import TensorSpec
 from .base import FeedForward
-from .linear import Linear, interleave_gate_up
+from .linear import SWIGLU_GROUP, Linear, interleave_gate_up
 
 
 class SwiGLU(FeedForward):
@@ -58,15 +58,29 @@ class SwiGLU(FeedForward):
         if name not in ops.ACTIVATIONS:
             raise UnsupportedError(f"activation {name!r}; the gated unit knows: " + ", ".join(sorted(ops.ACTIVATIONS)))
         self.activation = ops.ACTIVATIONS[name]
-        fused = interleave_gate_up(tensors[f"{prefix}.{gate}.weight"], tensors[f"{prefix}.{up}.weight"])
+        gate_w, up_w, down_w = (tensors[f"{prefix}.{n}.weight"] for n in (gate, up, down))
+        with_bias = bool(params.get("bias", False))
+        gate_b = tensors[f"{prefix}.{gate}.bias"].to(torch.float32) if with_bias else None
+        up_b = tensors[f"{prefix}.{up}.bias"].to(torch.float32) if with_bias else None
+        spare = -self.inter % SWIGLU_GROUP
+        if spare:
+            # Gate and up rows are interleaved in groups of 16.  An inner size that is no multiple
+            # of that is filled up with features whose rows, biases and down columns are zero: they
+            # come out as act(0) * 0 = 0 and add nothing.
+            rows = torch.zeros(spare, self.hidden, dtype=gate_w.dtype)
+            gate_w, up_w = torch.cat([gate_w, rows]), torch.cat([up_w, rows])
+            down_w = torch.cat([down_w, torch.zeros(self.hidden, spare, dtype=down_w.dtype)], dim=1)
+            if with_bias:
+                gate_b, up_b = (torch.cat([b, torch.zeros(spare)]) for b in (gate_b, up_b))
+            self.inter += spare
+        fused = interleave_gate_up(gate_w, up_w)
         fused_bias = down_bias = None
-        if params.get("bias", False):
+        if with_bias:
             # the bias of the interleaved rows, interleaved the same way
-            fused_bias = interleave_gate_up(tensors[f"{prefix}.{gate}.bias"].to(torch.float32)[:, None],
-                                            tensors[f"{prefix}.{up}.bias"].to(torch.float32)[:, None]).reshape(-1)
+            fused_bias = interleave_gate_up(gate_b[:, None], up_b[:, None]).reshape(-1)
             down_bias = tensors[f"{prefix}.{down}.bias"]
         self.gate_up = Linear(fused, dtype, device, bias=fused_bias)
-        self.down = Linear(tensors[f"{prefix}.{down}.weight"], dtype, device, bias=down_bias)
+        self.down = Linear(down_w, dtype, device, bias=down_bias)
 
     def kernel_families(self):
         return tuple(dict.fromkeys(self.gate_up.kernel_families() + self.down.kernel_families()))
