@@ -476,6 +476,187 @@ def measure_32b(peaks, warmup, page_size):
     return out
 
 
+# ---------------------------------------------------------------------------------------
+# --design nobupel: the Nobupel design beside the Qwen2 decoder at equal sizes
+# ---------------------------------------------------------------------------------------
+def nobupel_config(width, heads, kv_heads, ff, layers, vocab, cell_heads, cell_dim, cell_vdim, window=1024):
+    """`layers` layers in the design's usual proportion: three cells without a feed-forward, then
+    an attention layer with one; heads of 128 of which 64 values turn, a window that keeps 4 keys."""
+    cell = {"type": "mlstm", "mixer": {"heads": cell_heads, "dim": cell_dim, "vdim": cell_vdim, "gate_cap": 15.0},
+            "mlp": None}
+    attention = {"type": "attention", "mlp": {"kind": "dense", "ff": ff},
+                 "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                           "mask": {"size": window, "keep_first": 4},
+                           "rot": {"dims": 64, "base": 1000000.0,
+                                   "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+    return {"architecture": "Nobupel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "layers": [attention if index % 4 == 3 else cell for index in range(layers)], "loop": None}
+
+
+def qwen_like(width, heads, kv_heads, ff, layers, vocab):
+    return {"architectures": ["Qwen2ForCausalLM"], "num_hidden_layers": layers, "hidden_size": width,
+            "num_attention_heads": heads, "num_key_value_heads": kv_heads, "head_dim": 128, "intermediate_size": ff,
+            "vocab_size": vocab, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False,
+            "max_position_embeddings": 32768}
+
+
+DESIGN_SIZES = {
+    # name: width, heads, kv heads, inner size, layers, vocabulary, then the cell's heads, q/k size, value size
+    "1.5b-like": (1536, 12, 2, 8960, 8, 32000, 6, 128, 256),
+    "7b-like": (4096, 32, 8, 14336, 8, 32000, 8, 256, 512),
+}
+
+
+def nobupel_work(config, tokens, chunk=32):
+    """Floating-point operations of a prompt of `tokens` tokens by class of kernel (products of the
+    mixers, feed-forwards and output matrix; the cells' recurrence as the chunked form computes
+    it; attention within its window), and the bytes one decode step must move per class."""
+    width = config["width"]
+    flops = {"proj": 2.0 * config["vocab"] * width, "recurrence": 0.0, "attention": 0.0}
+    for layer in config["layers"]:
+        m = layer["mixer"]
+        if layer["type"] == "mlstm":
+            h, d, dv = m["heads"], m["dim"], m["vdim"]
+            flops["proj"] += 2.0 * tokens * width * (2 * h * d + 3 * h * dv + 2 * h)
+            # per token: scores and weighted values within the chunk (half of it masked), the read of S and its update
+            flops["recurrence"] += 2.0 * tokens * h * (chunk * (d + dv) / 2 + 2 * d * dv)
+        else:
+            h, g, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            flops["proj"] += 2.0 * tokens * width * (h * d + g * (d + dv) + h * dv)
+            seen = min(tokens, m["mask"]["size"]) if m.get("mask") else tokens
+            flops["attention"] += 2.0 * tokens * h * (d + dv) * (seen / 2 if seen == tokens else seen)
+        if layer.get("mlp"):
+            flops["proj"] += 2.0 * tokens * 3 * width * layer["mlp"]["ff"]
+    return flops
+
+
+def nobupel_decode_bytes(config, batch, history, element=2):
+    width = config["width"]
+    weights = config["vocab"] * width
+    state = cache = 0
+    for layer in config["layers"]:
+        m = layer["mixer"]
+        if layer["type"] == "mlstm":
+            h, d, dv = m["heads"], m["dim"], m["vdim"]
+            weights += width * (2 * h * d + 3 * h * dv + 2 * h)
+            state += 2 * batch * h * d * dv * 4            # the state is read and written, in 32-bit
+        else:
+            h, g, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            weights += width * (h * d + g * (d + dv) + h * dv)
+            seen = min(history, m["mask"]["size"] + m["mask"]["keep_first"]) if m.get("mask") else history
+            cache += batch * seen * g * (d + dv) * element
+        if layer.get("mlp"):
+            weights += 3 * width * layer["mlp"]["ff"]
+    return {"weights": weights * element, "state": state, "cache": cache}
+
+
+def profiled_prefill(model, tokens, page_size):
+    """One prompt launched kernel by kernel with an event behind every launch: milliseconds by class of kernel."""
+    from vipera_rs_b200.kernels import ops
+
+    ops.profile = ops.KernelProfile()
+    try:
+        measure_prefill(model, tokens, repeats=1, warmup=2, page_size=page_size)   # sizes seen, kernels loaded
+        ops.profile.totals.clear()
+        import numpy as np
+        import torch
+
+        from vipera_rs_b200.cache import CachePools
+        from vipera_rs_b200.engine import ModelRunner, StepInput
+
+        pools = CachePools(model.cache_requests, page_size=page_size, num_pages=-(-tokens // page_size) + 1,
+                           num_state_slots=1, dtype=model.dtype, device=model.device)
+        runner = ModelRunner(model, pools, max_model_len=model.spec.max_position_embeddings)
+        runner.step_graphs = runner.decode_graphs = False
+        prompt = np.random.default_rng(0).integers(0, model.spec.vocab_size, size=tokens, dtype=np.int32)
+        for _ in range(3):
+            pools.manager.open(0)
+            pools.manager.reserve(0, tokens)
+            step = StepInput(requests=[0], tokens=prompt, counts=[tokens], pos0=[0], fresh=[1],
+                             logit_rows=np.asarray([tokens - 1], dtype=np.int32))
+            torch.cuda.synchronize()
+            ops.profile.begin()
+            runner.run(step)
+            totals = ops.profile.end("prefill")
+            pools.manager.close(0)
+        return {name: round(value / totals["steps"], 4) for name, value in totals.items() if name != "steps"}
+    finally:
+        ops.profile = None
+
+
+def measure_design(args, peaks, peak_source):
+    """Prefill and decode of Nobupel at sizes that resemble real layers, beside the Qwen2 decoder of
+    the same width, heads, inner size and layer count; random weights, bfloat16."""
+    import torch  # noqa: F401
+
+    from vipera_rs_b200.engine import random_model
+
+    warmup = max(args.warmup, 3)
+    tokens = args.prefill_tokens
+    sampler = ClockSampler()
+    sampler.start()
+    sizes = {}
+    for name, (width, heads, kv_heads, ff, layers, vocab, cell_heads, cell_dim, cell_vdim) in DESIGN_SIZES.items():
+        if args.design_size and name != args.design_size:
+            continue
+        row = {}
+        for label, config in (("nobupel", nobupel_config(width, heads, kv_heads, ff, layers, vocab, cell_heads, cell_dim,
+                                                         cell_vdim)),
+                              ("qwen2", qwen_like(width, heads, kv_heads, ff, layers, vocab))):
+            model = random_model(config, seed=0, dtype="bfloat16", device="cuda:0")
+            out = {"layers": layers}
+            ms = measure_prefill(model, tokens, repeats=5, warmup=3, page_size=args.page_size)
+            out["prefill_ms"], out["prefill_tok_s"] = round(ms, 3), round(tokens * 1000.0 / ms, 1)
+            out["prefill_ms_by_class"] = profiled_prefill(model, tokens, args.page_size)
+            if label == "nobupel":
+                work = nobupel_work(config, tokens)
+                out["prefill_flops_by_class"] = {k: round(v / 1e9, 2) for k, v in work.items()}
+                out["prefill_frac_by_class"] = {
+                    k: round(v / (out["prefill_ms_by_class"][k] * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)
+                    for k, v in work.items() if out["prefill_ms_by_class"].get(k)}
+            else:
+                qc = dict(config, hidden_size=width)
+                out["prefill_frac"] = round(prefill_flops_head(qc, layers, tokens) / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)
+            for batch in (1, 8, 64):
+                harness = DecodeHarness(model, batch, args.history, args.steps + warmup + 2, page_size=args.page_size)
+                step_ms, mean_history = harness.timed(args.steps, warmup)
+                harness.close()
+                del harness
+                release_memory()
+                out[f"decode_b{batch}_tok_s"], out[f"decode_b{batch}_ms"] = round(batch * 1000.0 / step_ms, 1), round(step_ms, 4)
+                if label == "nobupel":
+                    moved = nobupel_decode_bytes(config, batch, mean_history)
+                    out[f"decode_b{batch}_hbm_frac"] = round(sum(moved.values()) / (step_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
+                else:
+                    out[f"decode_b{batch}_hbm_frac"] = round(
+                        decode_bytes_head(config, layers, batch, mean_history) / (step_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
+            row[label] = out
+            del model
+            release_memory()
+        sizes[name] = row
+    print(json.dumps({"design": "nobupel", "beside": "qwen2 at equal width, heads, inner size and layers",
+                      "dtype": "bf16", "data": "synthetic: seeded random weights, uniform random token ids",
+                      "prefill_tokens": tokens, "history": args.history, "steps": args.steps, "warmup": warmup,
+                      "peaks": peak_source, "sizes": sizes, "clocks": sampler.stop()}))
+    return 0
+
+
+def prefill_flops_head(config, layers, tokens):
+    """prefill_flops for a configuration that names its head size."""
+    h, d = config["hidden_size"], config.get("head_dim") or config["hidden_size"] // config["num_attention_heads"]
+    q, kv = config["num_attention_heads"] * d, config["num_key_value_heads"] * d
+    per_layer = h * (q + 2 * kv) + q * h + 3 * h * config["intermediate_size"]
+    return (2.0 * tokens * layers * per_layer + 2.0 * config["vocab_size"] * h
+            + 2.0 * tokens * tokens * d * config["num_attention_heads"] * layers)
+
+
+def decode_bytes_head(config, layers, batch, history, element=2):
+    h, d = config["hidden_size"], config.get("head_dim") or config["hidden_size"] // config["num_attention_heads"]
+    q, kv = config["num_attention_heads"] * d, config["num_key_value_heads"] * d
+    per_layer = h * (q + 2 * kv) + q * h + 3 * h * config["intermediate_size"]
+    return (layers * per_layer + config["vocab_size"] * h) * element + batch * history * 2 * layers * kv * element
+
+
 def plan_report(config, ctx, batch, device_bytes=180 * 10**9):
     """What `vipera plan` says about the shape at this context and batch (on one 180 GB device
     where nothing else is said)."""
@@ -504,6 +685,10 @@ def main():
     parser.add_argument("--prefill-tokens", type=int, default=2048)
     parser.add_argument("--skip-workloads", action="store_true",
                         help="leave out the 7B mixed workload and the 32B shape")
+    parser.add_argument("--design", choices=["nobupel"], default=None,
+                        help="instead of the headline: prefill and decode of that design at sizes that resemble "
+                             "real layers, beside the Qwen2 decoder at equal sizes")
+    parser.add_argument("--design-size", choices=sorted(DESIGN_SIZES), default=None, help="one of the sizes only")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -523,6 +708,8 @@ def main():
     from vipera_rs_b200.engine import random_model
 
     peaks, peak_source = read_peaks()
+    if args.design:
+        return measure_design(args, peaks, peak_source)
     shape_name, shape = SHAPES[args.config]
     full_layers = shape["num_hidden_layers"]
     config = dict(shape)

@@ -267,3 +267,49 @@ def test_greedy_generation_through_the_engine(dtype):
             margin = float(row.max() - row[token])
             assert margin <= (1e-4 if dtype == "float32" else 3e-2) * float(np.abs(row).max()), (index, token)
     assert engine.pools.audit() == ""
+
+
+def test_long_portions_with_all_chunks_at_once():
+    """Steps of 256 tokens and more compute the cells' chunks all at once (a block per chunk, the
+    states at the chunks' starts by a scan); shorter steps walk each entry's chunks.  Both forms
+    against the plain implementation, two unequal entries in a step, the second form's state
+    carried into the first's and into decoding."""
+    from vipera_rs_b200.parts.mlstm import MLSTM
+
+    dtype = "bfloat16"
+    path = folder_for("wide", dtype)
+    vocab = cases.CONFIGS["wide"]["vocab"]
+    a, b = helpers.random_tokens(vocab, 700, 91), helpers.random_tokens(vocab, 333, 92)
+    want = {"a": reference(path, a, dtype), "b": reference(path, b, dtype)}
+    outputs = {}
+    before = MLSTM.AT_ONCE_FROM
+    try:
+        for form, threshold in (("at once", 256), ("walking", 10 ** 9)):
+            MLSTM.AT_ONCE_FROM = threshold
+            rp = replayer(path, dtype, 1100, page_size=16)
+            judges = {name: Judge(dtype, want[name]) for name in want}
+            rows = []
+            got = rp.step([{"id": "a", "tokens": a[:450], "want": list(range(0, 450, 7))},
+                           {"id": "b", "tokens": b[:300], "want": list(range(0, 300, 5))}], [])
+            judges["a"].add(got[:len(range(0, 450, 7))], want["a"][0:450:7])
+            judges["b"].add(got[len(range(0, 450, 7)):], want["b"][0:300:5])
+            rows.append(got)
+            got = rp.step([{"id": "a", "tokens": a[450:690], "want": list(range(240))},     # 273 tokens: at once again
+                           {"id": "b", "tokens": b[300:333], "want": list(range(33))}], ["b"])
+            judges["a"].add(got[:240], want["a"][450:690])
+            judges["b"].add(got[240:], want["b"][300:333])
+            rows.append(got)
+            for position in range(690, 700):
+                got = rp.step([{"id": "a", "tokens": a[position:position + 1], "want": [0]}],
+                              ["a"] if position == 699 else [])
+                judges["a"].add(got[0], want["a"][position])
+                rows.append(got)
+            for judge in judges.values():
+                judge.close()
+            assert rp.pools.audit() == ""
+            outputs[form] = np.concatenate(rows)
+    finally:
+        MLSTM.AT_ONCE_FROM = before
+    difference = outputs["at once"] - outputs["walking"]
+    scale = np.sqrt((outputs["walking"].astype(np.float64) ** 2).mean())
+    assert np.sqrt((difference.astype(np.float64) ** 2).mean()) / scale <= 2e-2

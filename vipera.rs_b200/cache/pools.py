@@ -93,6 +93,7 @@ class CachePools:
         # One page beyond those the manager hands out, per group: the scratch page.  No request
         # ever holds it; tokens that pad a captured step to its size class write there.
         self.scratch_pages: List[int] = list(self.num_pages)
+        self.scratch_state_slot = int(num_state_slots)   # the spare row of every fixed-size state
         # Each pool lies between two guard regions of one page each, filled with a fixed word that
         # no kernel ever writes: `guards_intact()` (the tests call it after they ran) shows a write
         # that went past either end of a pool.
@@ -116,7 +117,8 @@ class CachePools:
                     *page_shape, group.v_dim)
                 self.views[slot] = PagedKVView(index, k, v, self.page_size, group.window, group.keep_first)
         for slot, request in self.states.items():
-            data = torch.zeros((int(num_state_slots), *request.shape), dtype=request.dtype, device=device)
+            # one row beyond the requests' own: the spare row, for entries that pad a captured step
+            data = torch.zeros((int(num_state_slots) + 1, *request.shape), dtype=request.dtype, device=device)
             self.views[slot] = StateView(data)
 
     def guards_intact(self) -> bool:

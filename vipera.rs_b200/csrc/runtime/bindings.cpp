@@ -202,8 +202,11 @@ PYBIND11_MODULE(_vipera_runtime, m) {
                out_tokens[i] = tok[from];
                out_positions[i] = pos[from];
                out_pos0[i] = pos[from];
-               out_slots[i] = c.state_slot(requests[from]);
-               out_fresh[i] = fr[from];
+               // an entry that pads the step works on the spare state row behind the requests' own,
+               // from nothing, so that no request's state moves twice
+               const bool own = i < static_cast<size_t>(n);
+               out_slots[i] = own ? c.state_slot(requests[from]) : c.num_state_slots();
+               out_fresh[i] = own ? fr[from] : 1;
              }
              for (int g = 0; g < c.num_groups(); ++g) {
                const int width = widths[g];

@@ -80,6 +80,22 @@ def _capture(forward):
     return graph, result
 
 
+def _warm_up(graph, ctx) -> None:
+    """Run a step once outside a graph before it is captured: buffers get their final sizes and
+    kernels are loaded.  Keys and values are written here and again, identically, by the replay.
+    A state of fixed size would move twice, so where the model keeps one this run works on the
+    spare state row, from nothing; the step's real rows come back with the staging copy."""
+    runner = graph.runner
+    has_state = bool(runner.pools.states)
+    if has_state:
+        graph._part(5).fill_(runner.pools.scratch_state_slot)
+        graph._part(6).fill_(1)
+    runner.forward(ctx)
+    if has_state:
+        graph.dev.copy_(graph.host, non_blocking=True)
+    torch.cuda.current_stream().synchronize()
+
+
 def _token_bucket(tokens: int) -> Optional[int]:
     for bucket in _TOKEN_BUCKETS:
         if tokens <= bucket:
@@ -410,10 +426,7 @@ class _DecodeGraph:
 
         runner = self.runner
         ctx = self._context()
-        # Once outside a graph: buffers get their final sizes, kernels are loaded.  The step's
-        # own keys and values are written here and again, identically, by the replay.
-        runner.forward(ctx)
-        torch.cuda.current_stream().synchronize()
+        _warm_up(self, ctx)
         before = ops.launches
         self.graph, self.logits = _capture(lambda: runner.forward(ctx))
         self.kernels = ops.launches - before
@@ -493,10 +506,11 @@ class _StepGraph:
         starts_h = part(3)
         starts_h[:own_entries + 1] = starts
         starts_h[own_entries + 1:] = t          # the padding entry ends the step; the rest bring nothing
-        for index, values in ((4, pos0), (5, slots), (6, fresh)):
+        # entries that pad the step start at position 0 on the spare state row, from nothing
+        for index, values, spare_value in ((4, pos0, 0), (5, slots, runner.pools.scratch_state_slot), (6, fresh, 1)):
             target = part(index)
             target[:own_entries] = values
-            target[own_entries:] = 0
+            target[own_entries:] = spare_value
         rows_h = part(7)
         if self.rows:
             rows_h[:rows.size] = rows
@@ -529,10 +543,7 @@ class _StepGraph:
         runner = self.runner
         if self.graph is None or self.stale():
             ctx = self._context()
-            # Once outside a graph: buffers get their final sizes, kernels are loaded.  The keys
-            # and values of the step are written here and again, identically, by the replay.
-            runner.forward(ctx)
-            torch.cuda.current_stream().synchronize()
+            _warm_up(self, ctx)
             before = ops.launches
             self.graph, self.logits = _capture(lambda: runner.forward(ctx))
             self.kernels = ops.launches - before

@@ -890,6 +890,7 @@ class _MlstmParams(ctypes.Structure):
         ("q_scale", _c_float), ("gate_cap", _c_float), ("denom_eps", _c_float),
         ("entry_starts", _c_void), ("state_slots", _c_void), ("fresh", _c_void), ("state", _c_void),
         ("state_stride", ctypes.c_longlong), ("o_raw", _c_void), ("nm_scratch", _c_void),
+        ("chunk_state", _c_void), ("chunk_n", _c_void), ("chunk_aux", _c_void), ("max_jobs", _c_int),
     ]
 
 
@@ -902,6 +903,14 @@ def mlstm_state_floats(heads: int, dim: int, vdim: int) -> int:
     return (heads * (dim * vdim + dim + 1) + 3) // 4 * 4
 
 
+MLSTM_CHUNK = 64   # tokens of a chunk in the tensor-core form (kTcChunk in mlstm.cu)
+
+
+def mlstm_tc_takes(dim: int, vdim: int) -> bool:
+    """Whether the tensor-core form of the cell's portions takes these sizes."""
+    return dim in (64, 128, 256)
+
+
 def mlstm_takes(dim: int, vdim: int) -> bool:
     fn = getattr(load_kernel_library("mlstm"), "vipera_mlstm_tile")
     fn.argtypes, fn.restype = [_c_int, _c_int], _c_int
@@ -911,15 +920,19 @@ def mlstm_takes(dim: int, vdim: int) -> bool:
 def mlstm(proj: torch.Tensor, *, offsets, heads: int, dim: int, vdim: int, q_scale: float, gate_cap: float,
           denom_eps: float, entry_starts: torch.Tensor, state_slots: torch.Tensor, fresh: torch.Tensor,
           token_entry: torch.Tensor, num_entries: int, single: bool, state: torch.Tensor, o_raw: torch.Tensor,
-          nm_scratch: torch.Tensor, norm_weight: torch.Tensor, norm_eps: float, out: torch.Tensor) -> None:
+          nm_scratch: torch.Tensor, norm_weight: torch.Tensor, norm_eps: float, out: torch.Tensor,
+          chunk_scratch=None) -> None:
     """The mLSTM cell over a step.  ``proj`` is the float32 product [tokens, width] that holds q, k,
     v, the output gate and the two gates' pre-activations at ``offsets`` (q, k, v, g, i, f);
     ``state`` is [slots, mlstm_state_floats]; ``out`` [tokens, heads * vdim] receives the cell's
     output after the head norm (times ``norm_weight``) and the output gate.  ``single`` promises
-    that every entry brings one token."""
+    that every entry brings one token.  ``chunk_scratch`` (float32 tensors: states [jobs, heads * d
+    * dv], n [jobs, heads * d], aux [jobs, heads * 4], with jobs >= tokens // MLSTM_CHUNK + entries)
+    lets a bfloat16 run compute all chunks of the step at once instead of walking each entry's."""
     global _mlstm_checked
     fn = _function("mlstm", "vipera_mlstm",
-                   [ctypes.POINTER(_MlstmParams), _c_int, _c_int, _c_void, _c_float, _c_void, _c_int, _c_void, _c_void])
+                   [ctypes.POINTER(_MlstmParams), _c_int, _c_int, _c_int, _c_void, _c_float, _c_void, _c_int, _c_void,
+                    _c_void])
     if not _mlstm_checked:
         size = _function("mlstm", "vipera_mlstm_params_size", [])()
         if size != ctypes.sizeof(_MlstmParams):
@@ -945,9 +958,22 @@ def mlstm(proj: torch.Tensor, *, offsets, heads: int, dim: int, vdim: int, q_sca
     p.state, p.state_stride = _gpu(state, "state", torch.float32), state.shape[1]
     p.o_raw = _gpu(o_raw, "o_raw", torch.float32)
     p.nm_scratch = _gpu(nm_scratch, "nm_scratch", torch.float32)
-    _check(fn(ctypes.byref(p), tokens, 1 if single else 0, _gpu(norm_weight, "norm_weight", torch.float32),
+    if chunk_scratch is not None:
+        states, ns, aux = chunk_scratch
+        jobs = states.shape[0]
+        if jobs < tokens // MLSTM_CHUNK + num_entries or ns.shape[0] < jobs or aux.shape[0] < jobs:
+            raise InvalidArgumentError("mlstm: the chunk scratch holds too few chunks for this step")
+        if states.shape[1] != heads * dim * vdim or ns.shape[1] != heads * dim or aux.shape[1] != heads * 4:
+            raise InvalidArgumentError("mlstm: the chunk scratch has the wrong row sizes")
+        p.chunk_state, p.chunk_n = _gpu(states, "chunk states", torch.float32), _gpu(ns, "chunk n", torch.float32)
+        p.chunk_aux, p.max_jobs = _gpu(aux, "chunk aux", torch.float32), tokens // MLSTM_CHUNK + num_entries
+    # a bfloat16 run's portions go through the tensor-core form where it takes the sizes
+    # (VIPERA_MLSTM_TC=0 keeps them on the CUDA cores)
+    tensor_cores = out.dtype == torch.bfloat16 and os.environ.get("VIPERA_MLSTM_TC", "1") != "0"
+    _check(fn(ctypes.byref(p), tokens, 1 if single else 0, 1 if tensor_cores else 0,
+              _gpu(norm_weight, "norm_weight", torch.float32),
               float(norm_eps), _gpu(out, "out"), dtype_code(out.dtype), _gpu(token_entry, "token_entry", torch.int32),
-              _stream()), "mlstm", kernels=2)
+              _stream()), "mlstm", kernels=4 if (chunk_scratch is not None and tensor_cores and not single) else 2)
 
 
 def kernel_status_word(device) -> torch.Tensor:

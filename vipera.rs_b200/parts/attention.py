@@ -184,10 +184,11 @@ class GQAttention(Mixer):
         heads, kv_heads, d = self.num_heads, self.num_kv_heads, self.head_dim
         window = self.window or 0
         if (ctx.dtype == torch.bfloat16 and d in ops.MMA_HEAD_DIMS and self.value_dim == d
-                and (self.keep_first or self.sink) and not ctx.all_single):
+                and (self.keep_first or self.sink)):
             # kept first keys and the sink are known to the mma.sync flash kernel, which then takes
-            # every entry of the step, those of one token too; steps of single tokens only take
-            # the general kernel below
+            # every entry of the step, those of one token too (a tile of queries with one row: the
+            # keys of its window stream through in tiles of 64, which at a window of a thousand keys
+            # is forty times faster than the general kernel's warp per head)
             ops.attention_prefill(q, mixed, cache.k, cache.v, entry_starts=ctx.entry_starts,
                                   entry_pos0=ctx.entry_pos0, block_table=table, num_entries=ctx.num_entries,
                                   num_heads=heads, num_kv_heads=kv_heads, head_dim=d, scale=self.scale,

@@ -64,8 +64,9 @@ class PagedKVView:
 
 
 class StateView:
-    """The state of one cache slot: ``data`` is [state_slots, *shape]; a request's row is
-    ``ctx.state_slots[entry]``, and ``ctx.fresh[entry]`` says that it must start anew."""
+    """The state of one cache slot: ``data`` is [state_slots + 1, *shape]; a request's row is
+    ``ctx.state_slots[entry]``, and ``ctx.fresh[entry]`` says that it must start anew.  The last
+    row is a spare that no request owns: entries that pad a captured step work on it."""
 
     def __init__(self, data: torch.Tensor):
         self.data = data

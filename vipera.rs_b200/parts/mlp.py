@@ -67,11 +67,12 @@ class SwiGLU(FeedForward):
             # Gate and up rows are interleaved in groups of 16.  An inner size that is no multiple
             # of that is filled up with features whose rows, biases and down columns are zero: they
             # come out as act(0) * 0 = 0 and add nothing.
-            rows = torch.zeros(spare, self.hidden, dtype=gate_w.dtype)
+            where = gate_w.device
+            rows = torch.zeros(spare, self.hidden, dtype=gate_w.dtype, device=where)
             gate_w, up_w = torch.cat([gate_w, rows]), torch.cat([up_w, rows])
-            down_w = torch.cat([down_w, torch.zeros(self.hidden, spare, dtype=down_w.dtype)], dim=1)
+            down_w = torch.cat([down_w, torch.zeros(self.hidden, spare, dtype=down_w.dtype, device=where)], dim=1)
             if with_bias:
-                gate_b, up_b = (torch.cat([b, torch.zeros(spare)]) for b in (gate_b, up_b))
+                gate_b, up_b = (torch.cat([b, torch.zeros(spare, device=where)]) for b in (gate_b, up_b))
             self.inter += spare
         fused = interleave_gate_up(gate_w, up_w)
         fused_bias = down_bias = None

@@ -17,6 +17,8 @@ chunk by chunk, single tokens in one pass over the state).
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..config.registry import MIXERS
@@ -34,6 +36,10 @@ class MLSTM(Mixer):
 
     kernels = ("mlstm",)
     takes_lazy_input = True
+    # Steps of this many tokens and more compute all chunks at once, as long as the states at the
+    # chunks' starts (32-bit, one per chunk and head) fit this many bytes.
+    AT_ONCE_FROM = int(os.environ.get("VIPERA_MLSTM_AT_ONCE_FROM", 256))
+    AT_ONCE_MOST_BYTES = 4 << 30
 
     @staticmethod
     def _names(params):
@@ -75,9 +81,10 @@ class MLSTM(Mixer):
         # Rows of q, k, v, g, then i and f, padded with zero rows to a multiple of 8.
         total = sum(widths)
         padded = (total + 7) // 8 * 8
-        fused = torch.cat(rows + ([torch.zeros(padded - total, self.hidden, dtype=rows[0].dtype)] if padded > total else []),
-                          dim=0)
-        bias = torch.zeros(padded, dtype=torch.float32)
+        where = rows[0].device    # tensors may come from a file (host) or from a generator on the device
+        spare = [torch.zeros(padded - total, self.hidden, dtype=rows[0].dtype, device=where)] if padded > total else []
+        fused = torch.cat(rows + spare, dim=0)
+        bias = torch.zeros(padded, dtype=torch.float32, device=where)
         offsets, at = [], 0
         for name, width in zip(names, widths):
             offsets.append(at)
@@ -111,12 +118,21 @@ class MLSTM(Mixer):
         o_raw = ws.get("mlstm.cell", (count, self.heads * self.vdim), torch.float32)
         scratch = ws.get("mlstm.nm", (ctx.num_entries, self.heads * (self.dim + 1)), torch.float32)
         mixed = ws.get("mlstm.out", (count, self.heads * self.vdim), ctx.dtype)
+        chunk_scratch = None
+        jobs = count // ops.MLSTM_CHUNK + ctx.num_entries
+        if (ctx.dtype == torch.bfloat16 and not ctx.all_single and count >= self.AT_ONCE_FROM
+                and ops.mlstm_tc_takes(self.dim, self.vdim) and self.vdim % 4 == 0
+                and jobs * self.heads * self.dim * self.vdim * 4 <= self.AT_ONCE_MOST_BYTES):
+            # a long step: all its chunks at once (a block per chunk) instead of each entry's one after another
+            chunk_scratch = (ws.get("mlstm.chunk_states", (jobs, self.heads * self.dim * self.vdim), torch.float32),
+                             ws.get("mlstm.chunk_n", (jobs, self.heads * self.dim), torch.float32),
+                             ws.get("mlstm.chunk_aux", (jobs, self.heads * 4), torch.float32))
         ops.mlstm(proj, offsets=self.offsets, heads=self.heads, dim=self.dim, vdim=self.vdim,
                   q_scale=self.dim ** -0.5, gate_cap=self.gate_cap, denom_eps=self.denominator_eps,
                   entry_starts=ctx.entry_starts, state_slots=ctx.state_slots, fresh=ctx.fresh,
                   token_entry=ctx.token_entry, num_entries=ctx.num_entries, single=ctx.all_single,
                   state=cache.data, o_raw=o_raw, nm_scratch=scratch, norm_weight=self.norm_weight,
-                  norm_eps=self.norm_eps, out=mixed)
+                  norm_eps=self.norm_eps, out=mixed, chunk_scratch=chunk_scratch)
         self.out(ctx, mixed, epilogue=ops.EPI_RESIDUAL, resid=residual)
 
 

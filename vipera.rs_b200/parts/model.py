@@ -79,16 +79,14 @@ class DecoderModel:
 
     @property
     def graph_safe(self) -> bool:
-        """Whether decode steps of this model may be captured in CUDA graphs: every part must
-        launch device work only, and no mixer may keep per-request state (padding a graph's
-        batch with copies of an entry would update such a state twice)."""
-        from .base import FixedState
-
+        """Whether steps of this model may be captured in CUDA graphs: every part must launch
+        device work only.  A mixer with per-request state qualifies when it touches only the
+        state rows the step names: entries that pad a captured step name the spare row."""
         for block in self.blocks:
             for part in block.parts():
                 if not getattr(part, "graph_safe", True):
                     return False
-        return not any(isinstance(request, FixedState) for request in self.cache_requests.values())
+        return True
 
     def kernel_families(self) -> List[str]:
         names = ["rowwise", *self.head.kernel_families()]
