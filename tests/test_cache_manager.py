@@ -266,7 +266,7 @@ def test_random_orders_with_shared_prefixes(seed):
 def test_decode_step_inputs_are_filled_in_the_graphs_layout():
     """The native routine behind the decode graphs: tokens, positions, state slots, fresh marks
     and block tables of the step's requests in one buffer, entries past the step's own
-    repeating its first; -1 for a step that is not a plain decode step; errors for a token
+    repeating its first (on the spare state row); -1 for a step that is not a plain decode step; errors for a token
     outside the vocabulary, a position past the limit, and a position without a page."""
     cache = manager([(16, 8, 0), (8, 8, 0)], slots=4)
     for request, length in ((5, 20), (9, 3)):
@@ -286,8 +286,9 @@ def test_decode_step_inputs_are_filled_in_the_graphs_layout():
     assert buffer[b:2 * b].tolist() == [19, 2, 19, 19]                  # positions
     assert buffer[2 * b:4 * b + 1].tolist() == [-7] * (2 * b + 1)       # the caller's constant parts
     assert buffer[4 * b + 1:5 * b + 1].tolist() == [19, 2, 19, 19]      # first positions
-    assert buffer[5 * b + 1:6 * b + 1].tolist() == [0, 1, 0, 0]         # state slots
-    assert buffer[6 * b + 1:7 * b + 1].tolist() == [0, 1, 0, 0]         # fresh
+    # entries that pad the step work on the spare state row behind the four slots, from nothing
+    assert buffer[5 * b + 1:6 * b + 1].tolist() == [0, 1, 4, 4]         # state slots
+    assert buffer[6 * b + 1:7 * b + 1].tolist() == [0, 1, 1, 1]         # fresh
     assert buffer[7 * b + 1:8 * b + 1].tolist() == [-7] * b
     first = buffer[8 * b + 1:8 * b + 1 + b * 2].reshape(b, 2)
     assert first.tolist() == [cache.table(5, 0).tolist(), cache.table(9, 0).tolist() + [-1]] + [cache.table(5, 0).tolist()] * 2

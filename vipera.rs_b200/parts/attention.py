@@ -95,7 +95,7 @@ class GQAttention(Mixer):
         own = ["rope_cache", "attention"]
         if self.dtype == torch.bfloat16 and self.head_dim in (64, 128) and self.value_dim == self.head_dim:
             own.append("attention_mma")
-            if self.head_dim in ops.TC_ATTENTION_HEAD_DIMS:
+            if self.head_dim in ops.TC_ATTENTION_HEAD_DIMS and not self.keep_first and not self.sink:
                 own.append("attention_tc")
         return tuple(dict.fromkeys(tuple(own) + self.qkv.kernel_families() + self.out.kernel_families()
                                    + self.position.kernel_families()))
