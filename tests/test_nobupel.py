@@ -160,3 +160,23 @@ def test_plain_attention_sink_window_and_kept_keys():
             scores = torch.cat([(k[seen] @ q[i, head]) * 0.9, torch.zeros(1, dtype=torch.float64)])   # the sink last
             out[i, head] = torch.softmax(scores, 0)[:-1] @ v[seen]
     assert float((got - out.reshape(count, 12) @ w["o"].T).abs().max()) < 1e-12
+
+
+def test_command_line_on_a_nobupel_folder():
+    """model-info and plan as a process, on a folder in the design's own file names."""
+    import subprocess
+    import sys
+
+    path = cases.folder("mixed", "bfloat16")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    info = subprocess.run([sys.executable, os.path.join(root, "bin", "vipera"), "model-info", path, "--json"],
+                          capture_output=True, text=True, timeout=300)
+    assert info.returncode == 0, info.stderr
+    report = json.loads(info.stdout)
+    assert report["architecture"] == "Nobupel" and report["layer_count"] == 4 and report["scheduled_layers"] == 6
+    assert report["vocab_size"] == 301 and report["hidden_size"] == 96 and not report["tied_output"]
+    # keys and values of one token: the attention runs (layer 1 twice, layer 3 once), bfloat16
+    assert report["kv_bytes_per_token_bf16"] == 2 * (2 * 1 * (24 + 40) + 2 * (32 + 16))
+    plan = subprocess.run([sys.executable, os.path.join(root, "bin", "vipera"), "plan", path, "--ctx", "512", "--batch", "3"],
+                          capture_output=True, text=True, timeout=300)
+    assert plan.returncode == 0 and "feasible                 True" in plan.stdout, plan.stdout + plan.stderr

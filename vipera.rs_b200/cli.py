@@ -79,11 +79,13 @@ def _model_report(model_dir: str) -> dict:
     from .config import load_config
     from .engine import planner
     from .parts import model_schema
-    from .weights import SafetensorsSource, check_source
+    from .weights import AliasedSource, SafetensorsSource, check_source
 
     arch, config = load_config(model_dir)
     spec = arch.model_spec(config)
     source = SafetensorsSource(model_dir)
+    if arch.tensor_alias is not None:
+        source = AliasedSource(source, arch.tensor_alias)
     schema = model_schema(spec)
     check_source(schema, source)
     dtypes, total_bytes, parameters = {}, 0, 0

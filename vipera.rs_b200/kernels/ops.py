@@ -242,6 +242,8 @@ def rope_cache(qkv: torch.Tensor, q_out: torch.Tensor, *, num_heads: int, num_kv
     kv_heads * value_dim]."""
     value_dim = head_dim if value_dim is None else int(value_dim)
     rot_dims = head_dim if rot_dims is None else int(rot_dims)
+    if style == ROPE_NONE:
+        rot_dims = head_dim if head_dim % 2 == 0 else 0    # nothing turns; an odd head size takes the general form
     if value_dim != head_dim or rot_dims != head_dim:
         return _rope_cache_partial(qkv, q_out, num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim,
                                    value_dim=value_dim, rot_dims=rot_dims, positions=positions, cos=cos, sin=sin,
