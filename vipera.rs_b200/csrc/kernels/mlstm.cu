@@ -277,6 +277,16 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ uint32_t ld32(const __nv_bfloat16* p) { return *reinterpret_cast<const uint32_t*>(p); }
+// Four neighbouring 32-bit values: one 16-byte load where the caller knows the address to be aligned.
+__device__ __forceinline__ float4 load4(const float* at, bool wide) {
+  if (wide) return *reinterpret_cast<const float4*>(at);
+  return make_float4(at[0], at[1], at[2], at[3]);
+}
+// Whether every q and k row of the product's result starts on 16 bytes.
+__device__ __forceinline__ bool rows_wide(const MlstmParams& p) {
+  return ((reinterpret_cast<uintptr_t>(p.proj) & 15) == 0) && p.proj_width % 4 == 0 && p.q_off % 4 == 0 && p.k_off % 4 == 0 &&
+         p.dim % 4 == 0;
+}
 // A fragment (16 x 16) of a row-major array with `stride` elements a row, at (row0, k0).
 __device__ __forceinline__ void load_a(uint32_t (&a)[4], const __nv_bfloat16* base, int stride, int row0, int k0, int g, int tq) {
   const __nv_bfloat16* at = base + (row0 + g) * stride + k0 + 2 * tq;
@@ -322,6 +332,7 @@ mlstm_chunk_tc_kernel(const MlstmParams p) {
   float* scal = we + L;      // [0] the running m
 
   const int d = D, dv = p.vdim;
+  const bool wide = rows_wide(p);
   const int e = blockIdx.z, h = blockIdx.y, c0 = blockIdx.x * TW;
   const int cols = min(TW, dv - c0);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tq = lane & 3;
@@ -355,19 +366,23 @@ mlstm_chunk_tc_kernel(const MlstmParams p) {
     const int len = min(L, count - start);
     const float* rows = p.proj + static_cast<size_t>(t0 + start) * p.proj_width;
     __syncthreads();   // the chunk before is done with its tiles; S^T, n and m are in place
-    for (int item = tid; item < L * (D / 2); item += kTcThreads) {
-      const int t = item / (D / 2), dd = (item % (D / 2)) * 2;
-      float2 q = make_float2(0.0f, 0.0f), k = make_float2(0.0f, 0.0f);
+    for (int item = tid; item < L * (D / 4); item += kTcThreads) {
+      const int t = item / (D / 4), dd = (item % (D / 4)) * 4;
+      float4 q = make_float4(0.0f, 0.0f, 0.0f, 0.0f), k = q;
       if (t < len) {
         const float* row = rows + static_cast<size_t>(t) * p.proj_width;
-        q = make_float2(row[p.q_off + h * d + dd] * p.q_scale, row[p.q_off + h * d + dd + 1] * p.q_scale);
-        k = make_float2(row[p.k_off + h * d + dd], row[p.k_off + h * d + dd + 1]);
+        q = load4(row + p.q_off + h * d + dd, wide);
+        k = load4(row + p.k_off + h * d + dd, wide);
       }
-      const __nv_bfloat162 kb = __floats2bfloat162_rn(k.x, k.y);
-      *reinterpret_cast<__nv_bfloat162*>(Qs + t * QS + dd) = __floats2bfloat162_rn(q.x, q.y);
-      *reinterpret_cast<__nv_bfloat162*>(Ks + t * QS + dd) = kb;
-      Kt[dd * LS + t] = kb.x;
-      Kt[(dd + 1) * LS + t] = kb.y;
+      const __nv_bfloat162 k01 = __floats2bfloat162_rn(k.x, k.y), k23 = __floats2bfloat162_rn(k.z, k.w);
+      *reinterpret_cast<__nv_bfloat162*>(Qs + t * QS + dd) = __floats2bfloat162_rn(q.x * p.q_scale, q.y * p.q_scale);
+      *reinterpret_cast<__nv_bfloat162*>(Qs + t * QS + dd + 2) = __floats2bfloat162_rn(q.z * p.q_scale, q.w * p.q_scale);
+      *reinterpret_cast<__nv_bfloat162*>(Ks + t * QS + dd) = k01;
+      *reinterpret_cast<__nv_bfloat162*>(Ks + t * QS + dd + 2) = k23;
+      Kt[dd * LS + t] = k01.x;
+      Kt[(dd + 1) * LS + t] = k01.y;
+      Kt[(dd + 2) * LS + t] = k23.x;
+      Kt[(dd + 3) * LS + t] = k23.y;
     }
     for (int item = tid; item < L * TW; item += kTcThreads) {
       const int t = item / TW, c = item % TW;
@@ -614,6 +629,7 @@ mlstm_parts_kernel(const MlstmParams p) {
   float* we = lfs + L;                                         // [L] exp(a_s - A)
   float* scal = we + L;                                        // [0] A, [1] B
   const int d = D, dv = p.vdim;
+  const bool wide = rows_wide(p);
   const int h = blockIdx.y, c0 = blockIdx.x * TW, job = blockIdx.z;
   const int cols = min(TW, dv - c0);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tq = lane & 3;
@@ -654,15 +670,14 @@ mlstm_parts_kernel(const MlstmParams p) {
     }
   }
   __syncthreads();
-  for (int item = tid; item < L * (D / 2); item += kTcThreads) {
-    const int t = item / (D / 2), dd = (item % (D / 2)) * 2;
-    float2 k = make_float2(0.0f, 0.0f);
-    if (t < len) {
-      const float* row = rows + static_cast<size_t>(t) * p.proj_width;
-      k = make_float2(row[p.k_off + h * d + dd], row[p.k_off + h * d + dd + 1]);
-    }
+  for (int item = tid; item < L * (D / 4); item += kTcThreads) {
+    const int t = item / (D / 4), dd = (item % (D / 4)) * 4;
+    float4 k = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (t < len) k = load4(rows + static_cast<size_t>(t) * p.proj_width + p.k_off + h * d + dd, wide);
     Kt[dd * LS + t] = __float2bfloat16_rn(k.x);
     Kt[(dd + 1) * LS + t] = __float2bfloat16_rn(k.y);
+    Kt[(dd + 2) * LS + t] = __float2bfloat16_rn(k.z);
+    Kt[(dd + 3) * LS + t] = __float2bfloat16_rn(k.w);
   }
   for (int item = tid; item < L * TW; item += kTcThreads) {
     const int t = item / TW, c = item % TW;
@@ -793,7 +808,8 @@ mlstm_scan_kernel(const MlstmParams p) {
 template <int D>
 struct OutputsLayout {
   static constexpr int kQS = D + 8, kLS = kTcChunk + 8;
-  static constexpr size_t kBytes = (2 * static_cast<size_t>(kTcChunk) * kQS + kTcTile * kLS + kTcChunk * kLS + kTcTile * kQS) * 2 +
+  // (S^T takes K's place once the scores are done: two blocks fit an SM at the largest size)
+  static constexpr size_t kBytes = (2 * static_cast<size_t>(kTcChunk) * kQS + kTcTile * kLS + kTcChunk * kLS) * 2 +
                                    (D + 8 * kTcChunk + 8) * 4;
 };
 
@@ -810,8 +826,9 @@ mlstm_outputs_kernel(const MlstmParams p) {
   __nv_bfloat16* Ks = Qs + L * QS;                             // [L][QS]
   __nv_bfloat16* Vt = Ks + L * QS;                             // [TW][LS]
   __nv_bfloat16* Ws = Vt + TW * LS;                            // [L][LS]
-  __nv_bfloat16* St = Ws + L * LS;                             // [TW][QS]
-  float* ns = reinterpret_cast<float*>(St + TW * QS);          // [D] n at the chunk's start
+  __nv_bfloat16* St = Ks;                                      // [TW][QS] in K's place, after the scores
+  static_assert(kTcTile <= kTcChunk, "S^T must fit where K lay");
+  float* ns = reinterpret_cast<float*>(Ws + L * LS);           // [D] n at the chunk's start
   float* av = ns + D;
   float* Mv = av + L;
   float* bv = Mv + L;
@@ -820,6 +837,7 @@ mlstm_outputs_kernel(const MlstmParams p) {
   float* rs = lfs + L;       // [2][L]
   float* qn = rs + 2 * L;    // [L]
   const int d = D, dv = p.vdim;
+  const bool wide = rows_wide(p);
   const int h = blockIdx.y, c0 = blockIdx.x * TW, job = blockIdx.z;
   const int cols = min(TW, dv - c0);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tq = lane & 3;
@@ -830,31 +848,19 @@ mlstm_outputs_kernel(const MlstmParams p) {
   const float m0 = p.chunk_aux[(static_cast<size_t>(job) * p.heads + h) * 4 + 2];
   const float* S_start = p.chunk_state + (static_cast<size_t>(job) * p.heads + h) * d * dv;
   const float* n_start = p.chunk_n + (static_cast<size_t>(job) * p.heads + h) * d;
-  for (int item = tid; item < D * (TW / 4); item += kTcThreads) {
-    const int dd = item / (TW / 4), c = (item % (TW / 4)) * 4;
-    float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    if (c + 3 < cols) v = *reinterpret_cast<const float4*>(S_start + static_cast<size_t>(dd) * dv + c0 + c);
-    else {
-      float* lanes = reinterpret_cast<float*>(&v);
-      for (int i = 0; i < 4; ++i)
-        if (c + i < cols) lanes[i] = S_start[static_cast<size_t>(dd) * dv + c0 + c + i];
-    }
-    St[c * QS + dd] = __float2bfloat16_rn(v.x);
-    St[(c + 1) * QS + dd] = __float2bfloat16_rn(v.y);
-    St[(c + 2) * QS + dd] = __float2bfloat16_rn(v.z);
-    St[(c + 3) * QS + dd] = __float2bfloat16_rn(v.w);
-  }
   for (int dd = tid; dd < d; dd += kTcThreads) ns[dd] = n_start[dd];
-  for (int item = tid; item < L * (D / 2); item += kTcThreads) {
-    const int t = item / (D / 2), dd = (item % (D / 2)) * 2;
-    float2 q = make_float2(0.0f, 0.0f), k = make_float2(0.0f, 0.0f);
+  for (int item = tid; item < L * (D / 4); item += kTcThreads) {
+    const int t = item / (D / 4), dd = (item % (D / 4)) * 4;
+    float4 q = make_float4(0.0f, 0.0f, 0.0f, 0.0f), k = q;
     if (t < len) {
       const float* row = rows + static_cast<size_t>(t) * p.proj_width;
-      q = make_float2(row[p.q_off + h * d + dd] * p.q_scale, row[p.q_off + h * d + dd + 1] * p.q_scale);
-      k = make_float2(row[p.k_off + h * d + dd], row[p.k_off + h * d + dd + 1]);
+      q = load4(row + p.q_off + h * d + dd, wide);
+      k = load4(row + p.k_off + h * d + dd, wide);
     }
-    *reinterpret_cast<__nv_bfloat162*>(Qs + t * QS + dd) = __floats2bfloat162_rn(q.x, q.y);
+    *reinterpret_cast<__nv_bfloat162*>(Qs + t * QS + dd) = __floats2bfloat162_rn(q.x * p.q_scale, q.y * p.q_scale);
+    *reinterpret_cast<__nv_bfloat162*>(Qs + t * QS + dd + 2) = __floats2bfloat162_rn(q.z * p.q_scale, q.w * p.q_scale);
     *reinterpret_cast<__nv_bfloat162*>(Ks + t * QS + dd) = __floats2bfloat162_rn(k.x, k.y);
+    *reinterpret_cast<__nv_bfloat162*>(Ks + t * QS + dd + 2) = __floats2bfloat162_rn(k.z, k.w);
   }
   for (int item = tid; item < L * TW; item += kTcThreads) {
     const int t = item / TW, c = item % TW;
@@ -946,6 +952,22 @@ mlstm_outputs_kernel(const MlstmParams p) {
     sum += __shfl_xor_sync(0xffffffffu, sum, 1);
     sum += __shfl_xor_sync(0xffffffffu, sum, 2);
     if (part == 0) qn[t] = sum;
+  }
+  __syncthreads();
+  // the state at the chunk's start, transposed, where K lay
+  for (int item = tid; item < D * (TW / 4); item += kTcThreads) {
+    const int dd = item / (TW / 4), c = (item % (TW / 4)) * 4;
+    float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (c + 3 < cols) v = *reinterpret_cast<const float4*>(S_start + static_cast<size_t>(dd) * dv + c0 + c);
+    else {
+      float* lanes = reinterpret_cast<float*>(&v);
+      for (int i = 0; i < 4; ++i)
+        if (c + i < cols) lanes[i] = S_start[static_cast<size_t>(dd) * dv + c0 + c + i];
+    }
+    St[c * QS + dd] = __float2bfloat16_rn(v.x);
+    St[(c + 1) * QS + dd] = __float2bfloat16_rn(v.y);
+    St[(c + 2) * QS + dd] = __float2bfloat16_rn(v.z);
+    St[(c + 3) * QS + dd] = __float2bfloat16_rn(v.w);
   }
   __syncthreads();
   float O[4][4];
