@@ -55,7 +55,24 @@ ONLY_ATTENTION_PLAIN = config([attention_layer(size=None, rot_dims=0, scaling=Fa
 ONLY_MLSTM = config([mlstm_layer()])
 ONLY_FF = config([mlstm_layer(ff=56)])
 
-CONFIGS = {"mixed": MIXED, "wide": WIDE, "attention": ONLY_ATTENTION, "attention_plain": ONLY_ATTENTION_PLAIN,
+# Values that the other configurations make equal, even, or absent: a width that is no multiple of
+# 8 (no tensor-core products), every key visible and no rotation at all, an odd head size, one head,
+# a window longer than any request, kept tokens beyond a page, a looped range that is empty, a cell
+# whose value size is no multiple of 4 with a q/k size the tensor-core form takes.
+ODD = config([attention_layer(heads=2, kv_heads=2, dim=40, vdim=24, scale=0.3, size=None, rot_dims=0, scaling=False, ff=100),
+              mlstm_layer(heads=1, dim=48, vdim=64, gate_cap=12.0),
+              attention_layer(heads=1, kv_heads=1, dim=17, vdim=9, scale=0.5, size=1000, keep_first=0, rot_dims=0,
+                              scaling=False),
+              attention_layer(heads=4, kv_heads=2, dim=16, vdim=16, scale=0.25, size=7, keep_first=21, rot_dims=8,
+                              scaling=True, ff=16)],
+             width=100, vocab=97, eps=1e-4, loop={"start": 2, "stop": 2, "times": 5})
+TENSOR = config([mlstm_layer(heads=2, dim=64, vdim=36, gate_cap=6.0, ff=48),
+                 mlstm_layer(heads=1, dim=256, vdim=96, gate_cap=20.0),
+                 attention_layer(heads=2, kv_heads=1, dim=128, vdim=128, scale=0.09, size=100, keep_first=70, rot_dims=128,
+                                 scaling=True, ff=None)],
+                width=200, vocab=211, eps=1e-6, loop={"start": 0, "stop": 3, "times": 2})
+
+CONFIGS = {"mixed": MIXED, "wide": WIDE, "odd": ODD, "tensor": TENSOR, "attention": ONLY_ATTENTION, "attention_plain": ONLY_ATTENTION_PLAIN,
            "mlstm": ONLY_MLSTM, "ff": ONLY_FF}
 # How the stored tensors are scaled (by the end of their names) so that the mechanisms show.
 SHARP = {".mix.q": 6.0, ".mix.k": 6.0, ".mix.i": 12.0, ".mix.f": 12.0, ".mix.v": 3.0, ".mlp.gate": 6.0}
