@@ -174,7 +174,10 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                         const int* __restrict__ block_table, int table_width, int page_size, int page_shift,
                         int num_heads, int num_kv_heads, float scale, int window, int chunk, int num_splits,
                         float* __restrict__ partial_ml, float* __restrict__ partial_out,
-                        const int* __restrict__ entry_starts) {
+                        const int* __restrict__ entry_starts, int keep_first) {
+  // keep_first (with a window): keys 0 .. keep_first-1 stay visible to every later query.  Those of
+  // them that the window has left behind are one more split, behind the num_splits of the window
+  // (blockIdx.z == num_splits): the partials have num_splits + 1 places per row then.
   constexpr int kKeys = 32;
   constexpr int kWarpTile = 2 * kKeys * D * 2;  // bytes of one warp's key and value tiles
   static_assert(16 * (D + 4) * 4 <= kWarpTile, "a warp's partial must fit in its tiles");
@@ -195,9 +198,14 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int position = positions[entry];
   const int* table = block_table + static_cast<size_t>(entry) * table_width;
-  const int first_visible = window > 0 ? max(0, position - window + 1) : 0;
-  const int begin = max(split * chunk, first_visible / kKeys * kKeys);
-  const int end = min((split + 1) * chunk, position + 1);
+  const int window_first = window > 0 ? max(0, position - window + 1) : 0;
+  const bool kept_split = split == num_splits;
+  const int places = num_splits + (keep_first > 0 ? 1 : 0);
+  // this split's visible keys are first_visible .. last_visible
+  const int first_visible = kept_split ? 0 : window_first;
+  const int last_visible = kept_split ? min(keep_first, window_first) - 1 : position;
+  const int begin = kept_split ? 0 : max(split * chunk, first_visible / kKeys * kKeys);
+  const int end = kept_split ? last_visible + 1 : min((split + 1) * chunk, position + 1);
   if (begin >= end) return;  // a split without visible keys: the combine kernel skips it too
 
   uint8_t* q_bytes = smem;                                        // [16][D] bf16, shared by the warps
@@ -254,7 +262,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
       for (int i = 0; i < 4; ++i) acc[n][i] = 0.0f;
     float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.0f, 0.0f};
     const int row_first[2] = {first_visible, first_visible};
-    const int row_limit[2] = {position, position};
+    const int row_limit[2] = {last_visible, last_visible};
     const float scale_log2 = scale * kLog2e;
 
     for (; key0 < end; key0 += 4 * kKeys) {
@@ -308,7 +316,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
           total += weight[w] * reinterpret_cast<const float*>(smem + 16 * D * 2 + w * kWarpTile)[row * (D + 4) + D + 1];
         }
         const int head = kv_head * group + head_in_group;
-        const size_t at = (static_cast<size_t>(entry) * num_heads + head) * num_splits + split;
+        const size_t at = (static_cast<size_t>(entry) * num_heads + head) * places + split;
         if (part == 0) {
           partial_ml[2 * at] = best;
           partial_ml[2 * at + 1] = total;
@@ -339,9 +347,12 @@ template <int D>
 __global__ void attention_combine_kernel(const float* __restrict__ partial_ml, const float* __restrict__ partial_out,
                                          int slices, __nv_bfloat16* __restrict__ out, int num_heads,
                                          const int* __restrict__ positions, int window, int chunk,
-                                         const int* __restrict__ entry_starts) {
-  __shared__ float maxima[128];
-  __shared__ float sums[128];
+                                         const int* __restrict__ entry_starts, int keep_first, int sink) {
+  // `slices` counts the window's splits; with kept first keys (keep_first > 0) each row has one
+  // more place, the last, for the kept keys the window has left behind.  sink != 0: a key of score
+  // 0 without a value joins the softmax, which adds exp2(-max) to the sum.
+  __shared__ float maxima[130];
+  __shared__ float sums[130];
   pdl_launch_dependents();
   // the step's description (written by the host before the step) is read before the wait
   const size_t row = static_cast<size_t>(blockIdx.x) * num_heads + blockIdx.y;
@@ -351,14 +362,20 @@ __global__ void attention_combine_kernel(const float* __restrict__ partial_ml, c
     if (entry_starts[blockIdx.x + 1] - token != 1) return;
     out_row = static_cast<size_t>(token) * num_heads + blockIdx.y;
   }
-  const float* ml = partial_ml + 2 * row * slices;
-  const float* values = partial_out + row * slices * D + threadIdx.x;
+  const int places = slices + (keep_first > 0 ? 1 : 0);
+  const float* ml = partial_ml + 2 * row * places;
+  const float* values = partial_out + row * places * D + threadIdx.x;
   // only the splits that hold visible keys were written by the decode kernel
   const int position = positions[blockIdx.x];
   pdl_wait();
   const int first_visible = window > 0 ? max(0, position - window + 1) : 0;
   const int first = (first_visible / 32 * 32) / chunk;
-  const int last = min(slices - 1, position / chunk);
+  const int window_last = min(slices - 1, position / chunk);
+  // the kept keys' split holds keys when the window has left some of them behind; it is folded in
+  // as the split after the window's last one (its partials are fetched from the row's last place)
+  const bool kept = keep_first > 0 && min(keep_first, first_visible) > 0;
+  const int last = window_last + (kept ? 1 : 0);
+  auto place_of = [&](int s) { return (kept && s == last) ? slices : s; };
   // Everything is asked for at once: this thread's column of every split's partial output (up to
   // kHeld of them stay in registers) beside all (max, sum) pairs, so that the combine costs one
   // trip to memory and not one per few splits; then the weights of the splits (at most 128 splits).
@@ -367,12 +384,12 @@ __global__ void attention_combine_kernel(const float* __restrict__ partial_ml, c
   float held[kHeld];
   if (count <= kHeld) {
 #pragma unroll
-    for (int i = 0; i < kHeld; ++i) held[i] = i < count ? values[static_cast<size_t>(first + i) * D] : 0.0f;
+    for (int i = 0; i < kHeld; ++i) held[i] = i < count ? values[static_cast<size_t>(place_of(first + i)) * D] : 0.0f;
   }
   float mine = -INFINITY;
   for (int s = first + threadIdx.x; s <= last; s += D) {
-    maxima[s] = ml[2 * s];
-    sums[s] = ml[2 * s + 1];
+    maxima[s] = ml[2 * place_of(s)];
+    sums[s] = ml[2 * place_of(s) + 1];
   }
   __syncthreads();
   for (int s = first; s <= last; ++s) mine = fmaxf(mine, maxima[s]);
@@ -393,9 +410,10 @@ __global__ void attention_combine_kernel(const float* __restrict__ partial_ml, c
       const float m = maxima[s];
       const float w = m == -INFINITY ? 0.0f : exp2f(m - mine);
       total += sums[s] * w;
-      value += values[static_cast<size_t>(s) * D] * w;
+      value += values[static_cast<size_t>(place_of(s)) * D] * w;
     }
   }
+  if (sink) total += exp2f(-mine);   // the maxima are in units of log2
   out[out_row * D + threadIdx.x] = __float2bfloat16_rn(value / total);
 }
 
@@ -711,7 +729,7 @@ template <int D>
 int launch_decode(const void* q, void* out, const void* k_pool, const void* v_pool, const int* positions,
                   const int* block_table, int table_width, int page_size, int num_entries, int num_heads,
                   int num_kv_heads, float scale, int window, int chunk, int num_splits, float* partial_ml,
-                  float* partial_out, const int* entry_starts, cudaStream_t s) {
+                  float* partial_out, const int* entry_starts, int keep_first, int sink, cudaStream_t s) {
   constexpr int kSmem = 16 * D * 2 + 4 * 2 * 32 * D * 2;
   int page_shift = -1;
   if ((page_size & (page_size - 1)) == 0) {
@@ -719,7 +737,7 @@ int launch_decode(const void* q, void* out, const void* k_pool, const void* v_po
     while ((1 << page_shift) < page_size) ++page_shift;
   }
   // the one-kernel forms serve steps of single tokens only
-  const ClusterChoice cluster = entry_starts ? ClusterChoice{0, false}
+  const ClusterChoice cluster = (entry_starts || keep_first > 0 || sink) ? ClusterChoice{0, false}
                                              : cluster_decode_choice(num_entries, num_heads, num_kv_heads, chunk * num_splits);
   if (cluster.blocks == 8 && cluster.prefetch)
     return launch_decode_cluster<D, 8, true>(q, out, k_pool, v_pool, positions, block_table, table_width, page_size,
@@ -739,15 +757,15 @@ int launch_decode(const void* q, void* out, const void* k_pool, const void* v_po
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  dim3 grid(num_entries, num_kv_heads, num_splits);
+  dim3 grid(num_entries, num_kv_heads, num_splits + (keep_first > 0 ? 1 : 0));
   int status = vipera_launch(attention_decode_kernel<D>, grid, 128, kSmem, s,
       static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_pool),
       static_cast<const __nv_bfloat16*>(v_pool), positions, block_table, table_width, page_size, page_shift,
-      num_heads, num_kv_heads, scale, window, chunk, num_splits, partial_ml, partial_out, entry_starts);
+      num_heads, num_kv_heads, scale, window, chunk, num_splits, partial_ml, partial_out, entry_starts, keep_first);
   if (status != VIPERA_OK) return status;
   return vipera_launch(attention_combine_kernel<D>, dim3(num_entries, num_heads), D, 0, s,
       static_cast<const float*>(partial_ml), static_cast<const float*>(partial_out), num_splits,
-      static_cast<__nv_bfloat16*>(out), num_heads, positions, window, chunk, entry_starts);
+      static_cast<__nv_bfloat16*>(out), num_heads, positions, window, chunk, entry_starts, keep_first, sink);
 }
 
 }  // namespace
@@ -807,17 +825,18 @@ VIPERA_API size_t vipera_attention_decode_scratch(int num_entries, int num_heads
 // first position), and entries of more tokens are skipped (vipera_attention_prefill with
 // skip_single runs those); q and out are then [tokens, heads, d] of the whole step.
 // The keys of an entry are cut into `num_splits` ranges of `chunk` keys (a multiple of 32).
-VIPERA_API int vipera_attention_decode(const void* q, void* out, const void* k_pool, const void* v_pool,
-                                       const int* positions, const int* block_table, int table_width, int page_size,
-                                       int num_entries, int num_heads, int num_kv_heads, int head_dim, float scale,
-                                       int window, int chunk, int num_splits, float* scratch, size_t scratch_floats,
-                                       const int* entry_starts, void* stream) {
+static int run_decode(const void* q, void* out, const void* k_pool, const void* v_pool, const int* positions,
+                      const int* block_table, int table_width, int page_size, int num_entries, int num_heads,
+                      int num_kv_heads, int head_dim, float scale, int window, int chunk, int num_splits, float* scratch,
+                      size_t scratch_floats, const int* entry_starts, int keep_first, int sink, void* stream) {
   if (num_entries <= 0) return VIPERA_OK;
-  if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads) return VIPERA_BAD_SHAPE;
+  if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads || keep_first < 0) return VIPERA_BAD_SHAPE;
   if (chunk <= 0 || chunk % 32 || num_splits <= 0 || num_splits > 128) return VIPERA_BAD_ARGUMENT;
-  const size_t need = vipera_attention_decode_scratch(num_entries, num_heads, head_dim, num_splits);
+  if (window <= 0) keep_first = 0;
+  const int places = num_splits + (keep_first > 0 ? 1 : 0);    // the kept keys are a split of their own
+  const size_t need = vipera_attention_decode_scratch(num_entries, num_heads, head_dim, places);
   if (!scratch || scratch_floats < need) return VIPERA_BAD_ARGUMENT;
-  const size_t rows = static_cast<size_t>(num_entries) * num_heads * num_splits;
+  const size_t rows = static_cast<size_t>(num_entries) * num_heads * places;
   float* partial_ml = scratch;
   float* partial_out = scratch + ((2 * rows + 3) / 4) * 4;
   if (reinterpret_cast<uintptr_t>(scratch) & 15) return VIPERA_BAD_ARGUMENT;
@@ -825,12 +844,35 @@ VIPERA_API int vipera_attention_decode(const void* q, void* out, const void* k_p
   if (head_dim == 128)
     return launch_decode<128>(q, out, k_pool, v_pool, positions, block_table, table_width, page_size, num_entries,
                               num_heads, num_kv_heads, scale, window, chunk, num_splits, partial_ml, partial_out,
-                              entry_starts, s);
+                              entry_starts, keep_first, sink, s);
   if (head_dim == 64)
     return launch_decode<64>(q, out, k_pool, v_pool, positions, block_table, table_width, page_size, num_entries,
                              num_heads, num_kv_heads, scale, window, chunk, num_splits, partial_ml, partial_out,
-                             entry_starts, s);
+                             entry_starts, keep_first, sink, s);
   return VIPERA_BAD_SHAPE;
+}
+
+VIPERA_API int vipera_attention_decode(const void* q, void* out, const void* k_pool, const void* v_pool,
+                                       const int* positions, const int* block_table, int table_width, int page_size,
+                                       int num_entries, int num_heads, int num_kv_heads, int head_dim, float scale,
+                                       int window, int chunk, int num_splits, float* scratch, size_t scratch_floats,
+                                       const int* entry_starts, void* stream) {
+  return run_decode(q, out, k_pool, v_pool, positions, block_table, table_width, page_size, num_entries, num_heads,
+                    num_kv_heads, head_dim, scale, window, chunk, num_splits, scratch, scratch_floats, entry_starts, 0, 0,
+                    stream);
+}
+
+// The same with kept first keys (`keep_first`, counts with a window only: the scratch then needs
+// num_splits + 1 places per row) and a sink (`sink` != 0).
+VIPERA_API int vipera_attention_decode_kept(const void* q, void* out, const void* k_pool, const void* v_pool,
+                                            const int* positions, const int* block_table, int table_width,
+                                            int page_size, int num_entries, int num_heads, int num_kv_heads,
+                                            int head_dim, float scale, int window, int chunk, int num_splits,
+                                            float* scratch, size_t scratch_floats, const int* entry_starts,
+                                            int keep_first, int sink, void* stream) {
+  return run_decode(q, out, k_pool, v_pool, positions, block_table, table_width, page_size, num_entries, num_heads,
+                    num_kv_heads, head_dim, scale, window, chunk, num_splits, scratch, scratch_floats, entry_starts,
+                    keep_first, sink, stream);
 }
 
 VIPERA_API const char* vipera_attention_mma_status_text(int status) { return vipera_status_text(status); }

@@ -1137,37 +1137,48 @@ mlstm_decode_kernel(const MlstmParams p) {
 // ---------------------------------------------------------------------------------------
 // the ending: head norm, scale, output gate; and the new n and m into the state
 // ---------------------------------------------------------------------------------------
-// One warp per (token, head).  out[t, h*dv + c] = o / rms(o) * weight[h*dv + c] * sigmoid(g[t, h*dv + c]).
+// One block per (token, head).  out[t, h*dv + c] = o / rms(o) * weight[h*dv + c] * sigmoid(g[t, h*dv + c]).
 template <typename T>
 __global__ void __launch_bounds__(128)
 mlstm_finish_kernel(const MlstmParams p, const float* __restrict__ weight, float eps, T* __restrict__ out,
                     const int* __restrict__ token_entry) {
+  __shared__ float scratch_sum[32];
   pdl_launch_dependents();
   pdl_wait();
-  const int t = blockIdx.x, lane = threadIdx.x & 31;
-  const int h = blockIdx.y * 4 + (threadIdx.x >> 5);
-  if (h >= p.heads) return;
+  const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
   const int dv = p.vdim, d = p.dim;
   const float* o = p.o_raw + (static_cast<size_t>(t) * p.heads + h) * dv;
-  float squares = 0.0f;
-  for (int c = lane; c < dv; c += 32) squares = fmaf(o[c], o[c], squares);
-  squares = warp_sum(squares);
-  const float inverse = rsqrtf(squares / static_cast<float>(dv) + eps);
   const float* gate = p.proj + static_cast<size_t>(t) * p.proj_width + p.g_off + h * dv;
+  // up to four values a thread stay in registers between the two passes (value sizes up to 512)
+  float mine[4], gates[4];
+  float squares = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int c = tid + 128 * i;
+    mine[i] = c < dv ? o[c] : 0.0f;
+    gates[i] = c < dv ? gate[c] : 0.0f;
+    squares = fmaf(mine[i], mine[i], squares);
+  }
+  for (int c = tid + 512; c < dv; c += 128) squares = fmaf(o[c], o[c], squares);
+  squares = block_sum(squares, scratch_sum);
+  const float inverse = rsqrtf(squares / static_cast<float>(dv) + eps);
   const float* w = weight + h * dv;
   T* dst = out + static_cast<size_t>(t) * p.heads * dv + h * dv;
-  for (int c = lane; c < dv; c += 32) {
-    const float g = 1.0f / (1.0f + expf(-gate[c]));
-    dst[c] = from_float<T>(o[c] * inverse * w[c] * g);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int c = tid + 128 * i;
+    if (c < dv) dst[c] = from_float<T>(mine[i] * inverse * w[c] * (1.0f / (1.0f + expf(-gates[i]))));
   }
+  for (int c = tid + 512; c < dv; c += 128)
+    dst[c] = from_float<T>(o[c] * inverse * w[c] * (1.0f / (1.0f + expf(-gate[c]))));
   const int e = token_entry[t];
   if (t == p.entry_starts[e + 1] - 1) {
     float* state = p.state + static_cast<long long>(p.state_slots[e]) * p.state_stride;
     float* n_state = state + static_cast<size_t>(p.heads) * d * dv + static_cast<size_t>(h) * d;
     float* m_state = state + static_cast<size_t>(p.heads) * d * (dv + 1) + h;
     const float* scratch = p.nm_scratch + (static_cast<size_t>(e) * p.heads + h) * (d + 1);
-    for (int dd = lane; dd < d; dd += 32) n_state[dd] = scratch[dd];
-    if (lane == 0) m_state[0] = scratch[d];
+    for (int dd = tid; dd < d; dd += 128) n_state[dd] = scratch[dd];
+    if (tid == 0) m_state[0] = scratch[d];
   }
 }
 
@@ -1243,7 +1254,7 @@ VIPERA_API int vipera_mlstm(const MlstmParams* params, int num_tokens, int singl
     status = vipera_launch(mlstm_chunk_kernel, grid, kThreads, shared, s, p);
   }
   if (status != 0) return status;
-  dim3 grid(num_tokens, (p.heads + 3) / 4);
+  dim3 grid(num_tokens, p.heads);
   if (out_dtype == VIPERA_F32)
     return vipera_launch(mlstm_finish_kernel<float>, grid, 128, 0, s, p, norm_weight, norm_eps, static_cast<float*>(out),
                          token_entry);

@@ -756,16 +756,19 @@ def decode_splits(num_entries: int, num_kv_heads: int, max_keys: int, sm_count: 
 def attention_decode(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, *,
                      positions: torch.Tensor, block_table: torch.Tensor, num_heads: int, num_kv_heads: int,
                      head_dim: int, scale: float, window: int, chunk: int, num_splits: int,
-                     scratch: torch.Tensor, entry_starts: Optional[torch.Tensor] = None) -> None:
+                     scratch: torch.Tensor, entry_starts: Optional[torch.Tensor] = None, keep_first: int = 0,
+                     sink: bool = False) -> None:
     """Split-key attention of the entries that bring one token (bfloat16, head sizes 64 and
     128); the partial results of the splits are combined by a second kernel.  Without
     ``entry_starts`` every entry brings one token (q and out are [entries, heads * d], positions
     one per entry).  With ``entry_starts`` [entries + 1] the step has portions too: q and out
     are [tokens, heads * d], ``positions`` holds each entry's first position, and entries of
-    more than one token are skipped (attention_prefill with ``skip_single`` runs them)."""
-    fn = _function("attention_mma", "vipera_attention_decode",
+    more than one token are skipped (attention_prefill with ``skip_single`` runs them).
+    ``keep_first`` (with a window: that many first keys stay visible; they are one more split, so
+    the scratch is sized for ``num_splits + 1``) and ``sink`` (one added to the softmax's denominator)."""
+    fn = _function("attention_mma", "vipera_attention_decode_kept",
                    [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int,
-                    _c_int, _c_float, _c_int, _c_int, _c_int, _c_void, ctypes.c_size_t, _c_void, _c_void])
+                    _c_int, _c_float, _c_int, _c_int, _c_int, _c_void, ctypes.c_size_t, _c_void, _c_int, _c_int, _c_void])
     if head_dim not in MMA_HEAD_DIMS:
         raise UnsupportedError(f"attention_decode: head size {head_dim} (built: 64, 128)")
     count = block_table.shape[0]
@@ -782,7 +785,7 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v
               _gpu(block_table, "block_table", torch.int32), block_table.shape[1], k_pool.shape[1], count,
               num_heads, num_kv_heads, head_dim, float(scale), int(window or 0), int(chunk), int(num_splits),
               _gpu(scratch, "scratch", torch.float32), scratch.numel(), _opt(entry_starts, "entry_starts", torch.int32),
-              _stream()), "attention_decode", kernels=2)
+              int(keep_first or 0) if window else 0, 1 if sink else 0, _stream()), "attention_decode", kernels=2)
 
 
 def attention_decode_scratch_floats(num_entries: int, num_heads: int, head_dim: int, num_splits: int) -> int:

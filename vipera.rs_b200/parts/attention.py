@@ -183,28 +183,21 @@ class GQAttention(Mixer):
         kernel otherwise; in every other case the general kernel."""
         heads, kv_heads, d = self.num_heads, self.num_kv_heads, self.head_dim
         window = self.window or 0
-        if (ctx.dtype == torch.bfloat16 and d in ops.MMA_HEAD_DIMS and self.value_dim == d
-                and (self.keep_first or self.sink)):
-            # kept first keys and the sink are known to the mma.sync flash kernel, which then takes
-            # every entry of the step, those of one token too (a tile of queries with one row: the
-            # keys of its window stream through in tiles of 64, which at a window of a thousand keys
-            # is forty times faster than the general kernel's warp per head)
-            ops.attention_prefill(q, mixed, cache.k, cache.v, entry_starts=ctx.entry_starts,
-                                  entry_pos0=ctx.entry_pos0, block_table=table, num_entries=ctx.num_entries,
-                                  num_heads=heads, num_kv_heads=kv_heads, head_dim=d, scale=self.scale,
-                                  window=window, keep_first=self.keep_first, sink=self.sink)
-            return
-        if (ctx.dtype == torch.bfloat16 and d in ops.MMA_HEAD_DIMS and self.value_dim == d
-                and not self.keep_first and not self.sink):
+        if ctx.dtype == torch.bfloat16 and d in ops.MMA_HEAD_DIMS and self.value_dim == d:
+            # Kept first keys and the sink are options of the mma.sync kernels (the flash kernel folds
+            # the kept keys as tiles of their own, the split-key kernel as a split of its own); the
+            # tcgen05 flash kernel serves attention without them.
+            kept = dict(keep_first=self.keep_first, sink=self.sink)
+            places = 1 if self.keep_first else 0
             if ctx.all_single:
                 chunk, splits = ops.decode_splits(ctx.num_entries, kv_heads, max(ctx.max_kv_len, 1),
                                                   ops.sm_count(q.device))
                 scratch = ctx.workspace.get(
                     "attention.partials",
-                    (ops.attention_decode_scratch_floats(ctx.num_entries, heads, d, splits),), torch.float32)
+                    (ops.attention_decode_scratch_floats(ctx.num_entries, heads, d, splits + places),), torch.float32)
                 ops.attention_decode(q, mixed, cache.k, cache.v, positions=ctx.positions, block_table=table,
                                      num_heads=heads, num_kv_heads=kv_heads, head_dim=d, scale=self.scale,
-                                     window=window, chunk=chunk, num_splits=splits, scratch=scratch)
+                                     window=window, chunk=chunk, num_splits=splits, scratch=scratch, **kept)
             else:
                 # portions through the flash kernel; the single tokens beside them (the running
                 # decodes of a mixed step) through the split-key kernel, which streams their
@@ -212,17 +205,17 @@ class GQAttention(Mixer):
                 ops.attention_prefill(q, mixed, cache.k, cache.v, entry_starts=ctx.entry_starts,
                                       entry_pos0=ctx.entry_pos0, block_table=table, num_entries=ctx.num_entries,
                                       num_heads=heads, num_kv_heads=kv_heads, head_dim=d, scale=self.scale,
-                                      window=window, skip_single=ctx.any_single)
+                                      window=window, skip_single=ctx.any_single, **kept)
                 if ctx.any_single:
                     chunk, splits = ops.decode_splits(ctx.num_entries, kv_heads, max(ctx.max_kv_len, 1),
                                                       ops.sm_count(q.device))
                     scratch = ctx.workspace.get(
                         "attention.partials",
-                        (ops.attention_decode_scratch_floats(ctx.num_entries, heads, d, splits),), torch.float32)
+                        (ops.attention_decode_scratch_floats(ctx.num_entries, heads, d, splits + places),), torch.float32)
                     ops.attention_decode(q, mixed, cache.k, cache.v, positions=ctx.entry_pos0, block_table=table,
                                          num_heads=heads, num_kv_heads=kv_heads, head_dim=d, scale=self.scale,
                                          window=window, chunk=chunk, num_splits=splits, scratch=scratch,
-                                         entry_starts=ctx.entry_starts)
+                                         entry_starts=ctx.entry_starts, **kept)
             return
         ops.attention(q, mixed, cache.k, cache.v, token_seq=ctx.token_entry, positions=ctx.positions,
                       block_table=table, num_heads=heads, num_kv_heads=kv_heads, head_dim=d,
