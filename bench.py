@@ -741,7 +741,8 @@ def main():
     sampler = ClockSampler()
     sampler.start()
 
-    harness = DecodeHarness(model, args.batch, args.history, args.steps + warmup, page_size=args.page_size)
+    # pages for the pass that captures the graphs (2 steps and its warm-up) and the timed pass
+    harness = DecodeHarness(model, args.batch, args.history, args.steps + 2 * warmup + 2, page_size=args.page_size)
     harness.timed(2, warmup)  # graphs captured, buffers sized
     launches_before = ops.launches
     ms_per_step, mean_history = harness.timed(args.steps, warmup)

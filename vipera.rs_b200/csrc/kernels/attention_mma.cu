@@ -167,7 +167,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
 // decode: block = (entry, KV head, split); rows of the tile = query heads of the group
 // ---------------------------------------------------------------------------------------
 // partial layout: [token][head][split]: max (log2 units), sum, and D unnormalised outputs.
-template <int D>
+template <int D, bool KEPT = false>   // KEPT: the instance that knows kept first keys (the other is the kernel as it was)
 __global__ void __launch_bounds__(128, 3)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
                         const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ positions,
@@ -199,8 +199,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   const int position = positions[entry];
   const int* table = block_table + static_cast<size_t>(entry) * table_width;
   const int window_first = window > 0 ? max(0, position - window + 1) : 0;
-  const bool kept_split = split == num_splits;
-  const int places = num_splits + (keep_first > 0 ? 1 : 0);
+  const bool kept_split = KEPT && split == num_splits;
+  const int places = num_splits + ((KEPT && keep_first > 0) ? 1 : 0);
   // this split's visible keys are first_visible .. last_visible
   const int first_visible = kept_split ? 0 : window_first;
   const int last_visible = kept_split ? min(keep_first, window_first) - 1 : position;
@@ -343,7 +343,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 }
 
 // grid: (tokens, heads); one block of D threads combines the splits of one row.
-template <int D>
+template <int D, bool KEPT = false>
 __global__ void attention_combine_kernel(const float* __restrict__ partial_ml, const float* __restrict__ partial_out,
                                          int slices, __nv_bfloat16* __restrict__ out, int num_heads,
                                          const int* __restrict__ positions, int window, int chunk,
@@ -362,7 +362,7 @@ __global__ void attention_combine_kernel(const float* __restrict__ partial_ml, c
     if (entry_starts[blockIdx.x + 1] - token != 1) return;
     out_row = static_cast<size_t>(token) * num_heads + blockIdx.y;
   }
-  const int places = slices + (keep_first > 0 ? 1 : 0);
+  const int places = slices + ((KEPT && keep_first > 0) ? 1 : 0);
   const float* ml = partial_ml + 2 * row * places;
   const float* values = partial_out + row * places * D + threadIdx.x;
   // only the splits that hold visible keys were written by the decode kernel
@@ -373,7 +373,7 @@ __global__ void attention_combine_kernel(const float* __restrict__ partial_ml, c
   const int window_last = min(slices - 1, position / chunk);
   // the kept keys' split holds keys when the window has left some of them behind; it is folded in
   // as the split after the window's last one (its partials are fetched from the row's last place)
-  const bool kept = keep_first > 0 && min(keep_first, first_visible) > 0;
+  const bool kept = KEPT && keep_first > 0 && min(keep_first, first_visible) > 0;
   const int last = window_last + (kept ? 1 : 0);
   auto place_of = [&](int s) { return (kept && s == last) ? slices : s; };
   // Everything is asked for at once: this thread's column of every split's partial output (up to
@@ -413,7 +413,7 @@ __global__ void attention_combine_kernel(const float* __restrict__ partial_ml, c
       value += values[static_cast<size_t>(place_of(s)) * D] * w;
     }
   }
-  if (sink) total += exp2f(-mine);   // the maxima are in units of log2
+  if (KEPT && sink) total += exp2f(-mine);   // the maxima are in units of log2
   out[out_row * D + threadIdx.x] = __float2bfloat16_rn(value / total);
 }
 
@@ -754,18 +754,31 @@ int launch_decode(const void* q, void* out, const void* k_pool, const void* v_po
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attention_decode_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  dim3 grid(num_entries, num_kv_heads, num_splits + (keep_first > 0 ? 1 : 0));
+  if (keep_first > 0 || sink) {
+    dim3 grid(num_entries, num_kv_heads, num_splits + (keep_first > 0 ? 1 : 0));
+    int status = vipera_launch(attention_decode_kernel<D, true>, grid, 128, kSmem, s,
+        static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_pool),
+        static_cast<const __nv_bfloat16*>(v_pool), positions, block_table, table_width, page_size, page_shift,
+        num_heads, num_kv_heads, scale, window, chunk, num_splits, partial_ml, partial_out, entry_starts, keep_first);
+    if (status != VIPERA_OK) return status;
+    return vipera_launch(attention_combine_kernel<D, true>, dim3(num_entries, num_heads), D, 0, s,
+        static_cast<const float*>(partial_ml), static_cast<const float*>(partial_out), num_splits,
+        static_cast<__nv_bfloat16*>(out), num_heads, positions, window, chunk, entry_starts, keep_first, sink);
+  }
+  dim3 grid(num_entries, num_kv_heads, num_splits);
   int status = vipera_launch(attention_decode_kernel<D>, grid, 128, kSmem, s,
       static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_pool),
       static_cast<const __nv_bfloat16*>(v_pool), positions, block_table, table_width, page_size, page_shift,
-      num_heads, num_kv_heads, scale, window, chunk, num_splits, partial_ml, partial_out, entry_starts, keep_first);
+      num_heads, num_kv_heads, scale, window, chunk, num_splits, partial_ml, partial_out, entry_starts, 0);
   if (status != VIPERA_OK) return status;
   return vipera_launch(attention_combine_kernel<D>, dim3(num_entries, num_heads), D, 0, s,
       static_cast<const float*>(partial_ml), static_cast<const float*>(partial_out), num_splits,
-      static_cast<__nv_bfloat16*>(out), num_heads, positions, window, chunk, entry_starts, keep_first, sink);
+      static_cast<__nv_bfloat16*>(out), num_heads, positions, window, chunk, entry_starts, 0, 0);
 }
 
 }  // namespace

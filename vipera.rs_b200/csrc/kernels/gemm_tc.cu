@@ -311,7 +311,9 @@ struct TileConfig {
 // ---------------------------------------------------------------------------------------
 // SWAP = false: accumulator rows are tokens, columns are features.
 // SWAP = true : accumulator rows are features, columns are tokens.
-template <int BN, bool SWAP>
+// EXT: the ending knows a bias outside the plain store and the gated unit's other activation; the
+// instances without it are the kernels as they were before those options existed.
+template <int BN, bool SWAP, bool EXT = false>
 __device__ __forceinline__ void finish_chunk(const GemmParams& p, const float* v, int width, int row, int col0) {
   // `row`: global index on the 128-row side; `col0`: global index of v[0] on the other side.
   const int N = p.features;
@@ -327,8 +329,12 @@ __device__ __forceinline__ void finish_chunk(const GemmParams& p, const float* v
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
         if (col0 + 16 + i >= N) break;
-        const float value = glu_mul(v[i] + (p.bias ? p.bias[col0 + i] : 0.0f),
-                                    v[16 + i] + (p.bias ? p.bias[col0 + 16 + i] : 0.0f), p.activation);
+        float value;
+        if constexpr (EXT)
+          value = glu_mul(v[i] + (p.bias ? p.bias[col0 + i] : 0.0f), v[16 + i] + (p.bias ? p.bias[col0 + 16 + i] : 0.0f),
+                          p.activation);
+        else
+          value = silu_mul(v[i], v[16 + i]);
         if (p.out_dtype == VIPERA_BF16) dst[i] = __float2bfloat16_rn(value); else dst32[i] = value;
       }
       return;
@@ -340,7 +346,8 @@ __device__ __forceinline__ void finish_chunk(const GemmParams& p, const float* v
       if (n >= N) break;
       const size_t at = static_cast<size_t>(t) * N + n;
       if (p.epilogue == EPI_RESIDUAL) {
-        p.resid[at] += v[i] + (p.bias ? p.bias[n] : 0.0f);
+        if constexpr (EXT) p.resid[at] += v[i] + (p.bias ? p.bias[n] : 0.0f);
+        else p.resid[at] += v[i];
       } else {
         const float value = v[i] + (p.bias ? p.bias[n] : 0.0f);
         if (p.out_dtype == VIPERA_BF16) static_cast<__nv_bfloat16*>(p.out)[at] = __float2bfloat16_rn(value);
@@ -354,15 +361,20 @@ __device__ __forceinline__ void finish_chunk(const GemmParams& p, const float* v
       // lanes 0-15 of a warp hold gate rows, lanes 16-31 the up rows of the same features
       const int inter = N >> 1;
       const int f = ((n - lane) >> 1) + (lane & 15);
-      const float own_bias = (p.bias && n < N) ? p.bias[n] : 0.0f;
-      const float other_bias = __shfl_xor_sync(0xffffffffu, own_bias, 16);
+      float own_bias = 0.0f, other_bias = 0.0f;
+      if constexpr (EXT) {
+        own_bias = (p.bias && n < N) ? p.bias[n] : 0.0f;
+        other_bias = __shfl_xor_sync(0xffffffffu, own_bias, 16);
+      }
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
         if (i >= width) break;
         const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
         const int t = col0 + i;
         if (lane < 16 && t < p.tokens && n + 16 < N) {
-          const float value = glu_mul(v[i] + own_bias, other + other_bias, p.activation);
+          float value;
+          if constexpr (EXT) value = glu_mul(v[i] + own_bias, other + other_bias, p.activation);
+          else value = silu_mul(v[i], other);
           const size_t at = static_cast<size_t>(t) * inter + f;
           if (p.out_dtype == VIPERA_BF16) static_cast<__nv_bfloat16*>(p.out)[at] = __float2bfloat16_rn(value);
           else static_cast<float*>(p.out)[at] = value;
@@ -371,7 +383,7 @@ __device__ __forceinline__ void finish_chunk(const GemmParams& p, const float* v
       return;
     }
     if (n >= N) return;
-    const float bias = p.bias ? p.bias[n] : 0.0f;
+    const float bias = ((EXT || p.epilogue == EPI_STORE) && p.bias) ? p.bias[n] : 0.0f;
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
       if (i >= width) break;
@@ -379,7 +391,7 @@ __device__ __forceinline__ void finish_chunk(const GemmParams& p, const float* v
       if (t >= p.tokens) break;
       const size_t at = static_cast<size_t>(t) * N + n;
       if (p.epilogue == EPI_RESIDUAL) {
-        p.resid[at] += v[i] + bias;
+        p.resid[at] += EXT ? v[i] + bias : v[i];
       } else {
         const float value = v[i] + bias;
         if (p.out_dtype == VIPERA_BF16) static_cast<__nv_bfloat16*>(p.out)[at] = __float2bfloat16_rn(value);
@@ -443,7 +455,7 @@ struct WorkLoop {
   }
 };
 
-template <int BN, bool SWAP, bool PAIR = false, bool EVEN = false>
+template <int BN, bool SWAP, bool PAIR = false, bool EVEN = false, bool EXT = false>
 __global__ void __launch_bounds__(threads_for<BN>(), (BN >= 128 || VIPERA_SMALL_BUDGET > 110 ? 1 : 2))
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
                const __grid_constant__ CUtensorMap map_out, const GemmParams p) {
@@ -821,18 +833,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
               for (int q4 = 0; q4 < 4; ++q4) {
                 float v[32];
                 tmem_load_32(taddr + c + q4 * 32, v);
-                if (p.bias) {
-#pragma unroll
-                  for (int i = 0; i < 32; ++i) {
-                    const int n = ty * BN + c + q4 * 32 + i;
-                    v[i] += n < p.features ? p.bias[n] : 0.0f;
-                  }
-                }
                 uint32_t packed[8];
+                if constexpr (EXT) {
+                  if (p.bias) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i)
-                  packed[i] = pack_bf16x2(glu_mul(v[2 * i], v[16 + 2 * i], p.activation),
-                                          glu_mul(v[2 * i + 1], v[16 + 2 * i + 1], p.activation));
+                    for (int i = 0; i < 32; ++i) {
+                      const int n = ty * BN + c + q4 * 32 + i;
+                      v[i] += n < p.features ? p.bias[n] : 0.0f;
+                    }
+                  }
+#pragma unroll
+                  for (int i = 0; i < 8; ++i)
+                    packed[i] = pack_bf16x2(glu_mul(v[2 * i], v[16 + 2 * i], p.activation),
+                                            glu_mul(v[2 * i + 1], v[16 + 2 * i + 1], p.activation));
+                } else {
+#pragma unroll
+                  for (int i = 0; i < 8; ++i)
+                    packed[i] = pack_bf16x2(silu_mul(v[2 * i], v[16 + 2 * i]), silu_mul(v[2 * i + 1], v[16 + 2 * i + 1]));
+                }
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                   const int chunk = (q4 * 2 + h) ^ (lane & 7);
@@ -863,7 +881,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 #pragma unroll
                 for (int i = 0; i < 32; ++i) v[i] += more[i];
               }
-              if (p.bias) {
+              if ((EXT || p.epilogue == EPI_STORE) && p.bias) {
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
                   const int n = ty * BN + c + i;
@@ -893,12 +911,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
           for (int c = 0; c < BN; c += 32) {
             float v[32];
             tmem_load_32(taddr + c, v);
-            finish_chunk<BN, SWAP>(p, v, 32, row, ty * BN + c);
+            finish_chunk<BN, SWAP, EXT>(p, v, 32, row, ty * BN + c);
           }
         } else {
           float v[32];
           tmem_load_16(taddr, v);
-          finish_chunk<BN, SWAP>(p, v, 16, row, ty * BN);
+          finish_chunk<BN, SWAP, EXT>(p, v, 16, row, ty * BN);
         }
         tcgen05_fence_before();
         __syncwarp();
@@ -962,7 +980,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 // are features, columns are tokens): one thread per output element adds the splits' partial
 // sums, split 0 first, and writes the ending.  Neighbouring threads take neighbouring
 // features, so the partial sums and the outputs are both read and written in whole lines.
-template <int BN>
+template <int BN, bool EXT = false>
 __global__ void __launch_bounds__(256)
 splitk_finish_kernel(const GemmParams p) {
   pdl_launch_dependents();
@@ -997,8 +1015,11 @@ splitk_finish_kernel(const GemmParams p) {
     return sum;
   };
   if (swiglu) {
-    const float value = glu_mul(total(n0) + (p.bias ? p.bias[n0] : 0.0f), total(n1) + (p.bias ? p.bias[n1] : 0.0f),
-                                p.activation);
+    float value;
+    if constexpr (EXT)
+      value = glu_mul(total(n0) + (p.bias ? p.bias[n0] : 0.0f), total(n1) + (p.bias ? p.bias[n1] : 0.0f), p.activation);
+    else
+      value = silu_mul(total(n0), total(n1));
     const size_t at = static_cast<size_t>(t) * width + o;
     if (p.out_dtype == VIPERA_BF16) static_cast<__nv_bfloat16*>(p.out)[at] = __float2bfloat16_rn(value);
     else static_cast<float*>(p.out)[at] = value;
@@ -1007,7 +1028,9 @@ splitk_finish_kernel(const GemmParams p) {
   const float value = total(n0);
   const size_t at = static_cast<size_t>(t) * N + o;
   if (p.epilogue == EPI_RESIDUAL) {
-    atomicAdd(p.resid + at, value + (p.bias ? p.bias[o] : 0.0f));   // one addition per element: no need to read the old value back
+    // one addition per element: no need to read the old value back
+    if constexpr (EXT) atomicAdd(p.resid + at, value + (p.bias ? p.bias[o] : 0.0f));
+    else atomicAdd(p.resid + at, value);
   } else {
     const float biased = value + (p.bias ? p.bias[o] : 0.0f);
     if (p.out_dtype == VIPERA_BF16) static_cast<__nv_bfloat16*>(p.out)[at] = __float2bfloat16_rn(biased);
@@ -1019,7 +1042,7 @@ splitk_finish_kernel(const GemmParams p) {
 // blocks that each make one trip to memory: a thread takes four neighbouring outputs of a token
 // (16-byte reads of the partial sums, one 16-byte write), a quarter of the threads.  A kernel of
 // its own, so that the few-token form stays as short as it is.
-template <int BN>
+template <int BN, bool EXT = false>
 __global__ void __launch_bounds__(256)
 splitk_finish4_kernel(const GemmParams p) {
   pdl_launch_dependents();
@@ -1054,16 +1077,19 @@ splitk_finish4_kernel(const GemmParams p) {
   const size_t at = static_cast<size_t>(t) * width + o;
   if (swiglu) {
     float4 up = total(n0 + 16);
-    if (p.bias) {
+    if (EXT && p.bias) {
       const float4 bg = *reinterpret_cast<const float4*>(p.bias + n0), bu = *reinterpret_cast<const float4*>(p.bias + n0 + 16);
       value = make_float4(value.x + bg.x, value.y + bg.y, value.z + bg.z, value.w + bg.w);
       up = make_float4(up.x + bu.x, up.y + bu.y, up.z + bu.z, up.w + bu.w);
     }
-    value = make_float4(glu_mul(value.x, up.x, p.activation), glu_mul(value.y, up.y, p.activation),
-                        glu_mul(value.z, up.z, p.activation), glu_mul(value.w, up.w, p.activation));
+    if constexpr (EXT)
+      value = make_float4(glu_mul(value.x, up.x, p.activation), glu_mul(value.y, up.y, p.activation),
+                          glu_mul(value.z, up.z, p.activation), glu_mul(value.w, up.w, p.activation));
+    else
+      value = make_float4(silu_mul(value.x, up.x), silu_mul(value.y, up.y), silu_mul(value.z, up.z), silu_mul(value.w, up.w));
   } else if (p.epilogue == EPI_RESIDUAL) {
     // one addition per element, nothing read back
-    if (p.bias) {
+    if (EXT && p.bias) {
       const float4 b = *reinterpret_cast<const float4*>(p.bias + o);
       value = make_float4(value.x + b.x, value.y + b.y, value.z + b.z, value.w + b.w);
     }
@@ -1462,7 +1488,12 @@ static GemmPlan make_plan(int T, int N, int K, int sms, int epilogue = EPI_STORE
 VIPERA_API int vipera_gemm_tc_workspace(int T, int N, int K, size_t* scratch_bytes) {
   const GemmPlan plan = make_plan(T, N, K, sm_count());
   const GemmPlan even = make_plan(T, N, K, sm_count(), EPI_RESIDUAL, true);
-  *scratch_bytes = std::max(plan.scratch_floats, even.scratch_floats) * sizeof(float);
+  // (the endings with a bias or another activation run without pairs of blocks)
+  const int pairs_before = pair_mode();
+  pair_mode() = 0;
+  const GemmPlan alone = make_plan(T, N, K, sm_count());
+  pair_mode() = pairs_before;
+  *scratch_bytes = std::max(std::max(plan.scratch_floats, even.scratch_floats), alone.scratch_floats) * sizeof(float);
   return VIPERA_OK;
 }
 
@@ -1491,17 +1522,17 @@ VIPERA_API int vipera_gemm_tc_plan(int T, int N, int K, int epilogue, int even_o
   return VIPERA_OK;
 }
 
-template <int BN, bool SWAP, bool EVEN = false>
+template <int BN, bool SWAP, bool EVEN = false, bool EXT = false>
 static int launch_variant(const CUtensorMap& map_x, const CUtensorMap& map_y, const CUtensorMap& map_out,
                           const GemmParams& p, int grid, cudaStream_t s) {
   using Config = TileConfig<BN>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, SWAP, false, EVEN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Config::kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, SWAP, false, EVEN, EXT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Config::kSmemBytes);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  int status = vipera_launch(gemm_tc_kernel<BN, SWAP, false, EVEN>, grid, threads_for<BN>(), Config::kSmemBytes, s, map_x, map_y, map_out, p);
+  int status = vipera_launch(gemm_tc_kernel<BN, SWAP, false, EVEN, EXT>, grid, threads_for<BN>(), Config::kSmemBytes, s, map_x, map_y, map_out, p);
   if (status != VIPERA_OK || p.splits == 1) return status;   // (even shares run with splits == 1)
   if (p.epilogue == EPI_ROPE_CACHE) {
     const long threads = static_cast<long>(p.tokens) * (p.num_heads + 2 * p.num_kv_heads) * (p.head_dim / 8);
@@ -1516,8 +1547,8 @@ static int launch_variant(const CUtensorMap& map_x, const CUtensorMap& map_y, co
   // has four times the loads in flight; measured 1.98 against 2.21 ms for a step of 128 tokens,
   // 2.86 against 2.80 for 512)
   if (outputs >= 600000 && width % 4 == 0 && aligned)
-    return vipera_launch(splitk_finish4_kernel<BN>, dim3(static_cast<unsigned>((outputs / 4 + 255) / 256)), dim3(256), 0, s, p);
-  return vipera_launch(splitk_finish_kernel<BN>, dim3(static_cast<unsigned>((outputs + 255) / 256)), dim3(256), 0, s, p);
+    return vipera_launch(splitk_finish4_kernel<BN, EXT>, dim3(static_cast<unsigned>((outputs / 4 + 255) / 256)), dim3(256), 0, s, p);
+  return vipera_launch(splitk_finish_kernel<BN, EXT>, dim3(static_cast<unsigned>((outputs + 255) / 256)), dim3(256), 0, s, p);
 }
 
 // Pairs of blocks: clusters of two, as many as fit on the device at once (a persistent loop).
@@ -1566,7 +1597,13 @@ static int run_gemm(const void* A, const void* W, int T, int N, int K, int epilo
   const bool even_ok = !direct_store && N % 4 == 0 && scratch != nullptr &&
       ((epilogue == EPI_STORE && out_dtype == VIPERA_F32 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) ||
        (epilogue == EPI_RESIDUAL && (reinterpret_cast<uintptr_t>(resid) & 15) == 0));
-  const GemmPlan plan = make_plan(T, N, K, sms, epilogue, even_ok);
+  // A bias outside the plain store, or the gated unit's other activation: the instances that know
+  // them exist for blocks alone with whole tiles or splits (no pairs, no even shares).
+  const bool ext = rope == nullptr && (activation != ACT_SILU || (bias != nullptr && epilogue != EPI_STORE));
+  const int pairs_before = pair_mode();
+  if (ext) pair_mode() = 0;
+  const GemmPlan plan = make_plan(T, N, K, sms, epilogue, even_ok && !ext);
+  pair_mode() = pairs_before;
   if (plan.splits > 1 || plan.even_shares) {
     if (!scratch || scratch_bytes < plan.scratch_floats * sizeof(float)) return VIPERA_BAD_ARGUMENT;
   }
@@ -1638,6 +1675,20 @@ static int run_gemm(const void* A, const void* W, int T, int N, int K, int epilo
   if (plan.even_shares) {
     if (plan.bn == 256) return launch_variant<256, false, true>(map_x, map_y, map_out, p, grid, s);
     return launch_variant<128, false, true>(map_x, map_y, map_out, p, grid, s);
+  }
+  if (ext) {
+    if (!plan.swap) {
+      if (plan.bn == 256) return launch_variant<256, false, false, true>(map_x, map_y, map_out, p, grid, s);
+      if (plan.bn == 192) return launch_variant<192, false, false, true>(map_x, map_y, map_out, p, grid, s);
+      return launch_variant<128, false, false, true>(map_x, map_y, map_out, p, grid, s);
+    }
+    switch (plan.bn) {
+      case 16: return launch_variant<16, true, false, true>(map_x, map_y, map_out, p, grid, s);
+      case 32: return launch_variant<32, true, false, true>(map_x, map_y, map_out, p, grid, s);
+      case 64: return launch_variant<64, true, false, true>(map_x, map_y, map_out, p, grid, s);
+      case 128: return launch_variant<128, true, false, true>(map_x, map_y, map_out, p, grid, s);
+      default: return launch_variant<256, true, false, true>(map_x, map_y, map_out, p, grid, s);
+    }
   }
   if (!plan.swap) {
     if (plan.bn == 256) return launch_variant<256, false>(map_x, map_y, map_out, p, grid, s);

@@ -94,6 +94,9 @@ struct Ending {
   int rotate;
 };
 
+// EXT: a bias outside the plain store and the gated unit's other activation; the instances without
+// it are the kernel as it was before those options existed.
+template <bool EXT>
 __device__ __forceinline__ Ending prepare_ending(const GemvParams& p, int row_lo, int row_hi, int t) {
   Ending e;
   e.bias_lo = e.bias_hi = 0.0f;
@@ -103,9 +106,9 @@ __device__ __forceinline__ Ending prepare_ending(const GemvParams& p, int row_lo
   e.active = 1;
   e.rotate = 0;
   const bool has_hi = row_hi < p.N;
-  if (p.epilogue != GEMV_ROPE_CACHE) {
+  if (p.epilogue == GEMV_STORE || (EXT && p.epilogue != GEMV_ROPE_CACHE)) {
     if (p.bias) { if (row_lo < p.N) e.bias_lo = p.bias[row_lo]; if (has_hi) e.bias_hi = p.bias[row_hi]; }
-  } else {
+  } else if (p.epilogue == GEMV_ROPE_CACHE) {
     if (p.bias) { e.bias_lo = p.bias[row_lo]; e.bias_hi = p.bias[row_hi]; }
     const int d = p.head_dim, half = d >> 1;
     const int head = row_lo / d, i = row_lo % d;
@@ -135,20 +138,30 @@ __device__ __forceinline__ Ending prepare_ending(const GemvParams& p, int row_lo
 }
 
 // One (row pair, token) result, finished and stored.
+template <bool EXT>
 __device__ __forceinline__ void finish(const GemvParams& p, const Ending& e, int row_lo, int row_hi, int t, float v_lo,
                                        float v_hi) {
   const bool has_hi = row_hi < p.N;
   if (p.epilogue == GEMV_RESIDUAL) {
     // every element of the stream gets one addition from one thread: an addition that does not
     // read the old value back gives the same sum and spares the ending a memory round trip
-    atomicAdd(p.resid + static_cast<size_t>(t) * p.N + row_lo, v_lo + e.bias_lo);
-    if (has_hi) atomicAdd(p.resid + static_cast<size_t>(t) * p.N + row_hi, v_hi + e.bias_hi);
+    if constexpr (EXT) {
+      v_lo += e.bias_lo;
+      v_hi += e.bias_hi;
+    }
+    atomicAdd(p.resid + static_cast<size_t>(t) * p.N + row_lo, v_lo);
+    if (has_hi) atomicAdd(p.resid + static_cast<size_t>(t) * p.N + row_hi, v_hi);
   } else if (p.epilogue == GEMV_SWIGLU) {
     const int feature = (row_lo >> 5) * 16 + (row_lo & 15);
-    v_lo += e.bias_lo;
-    v_hi += e.bias_hi;
-    const float value = p.activation == ACT_GELU_TANH ? v_hi * gate_activation(v_lo, ACT_GELU_TANH)
-                                                      : v_hi * (v_lo / (1.0f + __expf(-v_lo)));
+    float value;
+    if constexpr (EXT) {
+      v_lo += e.bias_lo;
+      v_hi += e.bias_hi;
+      value = p.activation == ACT_GELU_TANH ? v_hi * gate_activation(v_lo, ACT_GELU_TANH)
+                                            : v_hi * (v_lo / (1.0f + __expf(-v_lo)));
+    } else {
+      value = v_hi * (v_lo / (1.0f + __expf(-v_lo)));
+    }
     const size_t at = static_cast<size_t>(t) * (p.N >> 1) + feature;
     if (p.out_dtype == VIPERA_BF16) static_cast<__nv_bfloat16*>(p.out)[at] = __float2bfloat16_rn(value);
     else static_cast<float*>(p.out)[at] = value;
@@ -181,7 +194,7 @@ __device__ __forceinline__ void finish(const GemvParams& p, const Ending& e, int
 
 // NT: token tiles of 8 (tokens padded to NT * 8).  Block: 32 * warps threads; it stages the
 // activations once and then takes 16-row tiles blockIdx.x, blockIdx.x + gridDim.x, ...
-template <int NT, bool NORM>
+template <int NT, bool NORM, bool EXT = false>
 __global__ void __launch_bounds__(512)
 gemv_small_kernel(const GemvParams p, int num_tiles) {
   extern __shared__ __align__(16) uint8_t shared[];
@@ -229,7 +242,7 @@ gemv_small_kernel(const GemvParams p, int num_tiles) {
   if (one_item && my_t < p.T) {
     int out_lo, out_hi;
     tile_rows(p, tile, my_r, &out_lo, &out_hi);
-    if (out_lo < p.N) my_ending = prepare_ending(p, out_lo, out_hi, my_t);
+    if (out_lo < p.N) my_ending = prepare_ending<EXT>(p, out_lo, out_hi, my_t);
   }
   pdl_wait();
 
@@ -294,7 +307,7 @@ gemv_small_kernel(const GemvParams p, int num_tiles) {
     if (one_item && my_t < p.T) {
       int out_lo, out_hi;
       tile_rows(p, tile, my_r, &out_lo, &out_hi);
-      if (out_lo < p.N) my_ending = prepare_ending(p, out_lo, out_hi, my_t);
+      if (out_lo < p.N) my_ending = prepare_ending<EXT>(p, out_lo, out_hi, my_t);
     }
   }
   // ---- the products ----
@@ -374,19 +387,19 @@ gemv_small_kernel(const GemvParams p, int num_tiles) {
     int out_lo, out_hi;
     tile_rows(p, tile, r, &out_lo, &out_hi);
     if (out_lo < p.N) {
-      if (one_item) finish(p, my_ending, out_lo, out_hi, t, v_lo, v_hi);
-      else finish(p, prepare_ending(p, out_lo, out_hi, t), out_lo, out_hi, t, v_lo, v_hi);
+      if (one_item) finish<EXT>(p, my_ending, out_lo, out_hi, t, v_lo, v_hi);
+      else finish<EXT>(p, prepare_ending<EXT>(p, out_lo, out_hi, t), out_lo, out_hi, t, v_lo, v_hi);
     }
   }
   __syncthreads();  // the partials are read; the next tile may overwrite them
   }
 }
 
-template <int NT, bool NORM>
+template <int NT, bool NORM, bool EXT = false>
 static int launch_gemv(const GemvParams& p, int tiles, int warps, size_t shared, cudaStream_t s) {
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_small_kernel<NT, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemvMaxShared);
+    cudaError_t e = cudaFuncSetAttribute(gemv_small_kernel<NT, NORM, EXT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemvMaxShared);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
@@ -403,7 +416,7 @@ static int launch_gemv(const GemvParams& p, int tiles, int warps, size_t shared,
   if (per_sm > 2048 / (warps * 32)) per_sm = 2048 / (warps * 32);
   int blocks = sms * per_sm;
   if (blocks > tiles) blocks = tiles;
-  return vipera_launch(gemv_small_kernel<NT, NORM>, dim3(blocks), dim3(warps * 32), shared, s, p, tiles);
+  return vipera_launch(gemv_small_kernel<NT, NORM, EXT>, dim3(blocks), dim3(warps * 32), shared, s, p, tiles);
 }
 
 // Token tiles of 8 the kernel is built for: 1, 2, 4 or 8.
@@ -463,7 +476,13 @@ VIPERA_API int vipera_gemv_small(const GemvParams* params, void* stream) {
   const size_t shared = gemv_shared_bytes(p.T, p.K, warps);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int nt = gemv_token_tiles(p.T);
-#define VIPERA_GEMV_CASE(NT)                                                               \
+  // a bias outside the plain store, or the gated unit's other activation: the instances that know them
+  const bool ext = (p.epilogue == GEMV_SWIGLU && (p.bias != nullptr || p.activation != ACT_SILU)) ||
+                   (p.epilogue == GEMV_RESIDUAL && p.bias != nullptr);
+#define VIPERA_GEMV_CASE(NT)                                                                                   \
+  if (ext)                                                                                                     \
+    return p.x32 ? launch_gemv<NT, true, true>(p, tiles, warps, shared, s)                                     \
+                 : launch_gemv<NT, false, true>(p, tiles, warps, shared, s);                                   \
   return p.x32 ? launch_gemv<NT, true>(p, tiles, warps, shared, s) : launch_gemv<NT, false>(p, tiles, warps, shared, s)
   if (nt == 1) { VIPERA_GEMV_CASE(1); }
   if (nt == 2) { VIPERA_GEMV_CASE(2); }
