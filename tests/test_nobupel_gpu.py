@@ -353,3 +353,28 @@ def test_other_sizes(name, dtype):
     for judge in judges.values():
         judge.close()
     assert rp.pools.audit() == "" and rp.pools.manager.free_state_slots == 4
+
+
+def test_generate_from_the_command_line():
+    """bin/vipera generate on a Nobupel folder: the greedy continuation is the engine's own, and
+    each of its tokens is the plain implementation's best (or within rounding of it)."""
+    import os
+    import subprocess
+    import sys
+
+    path = cases.folder("wide", "bfloat16", scaling="none")
+    prompt = [5, 17, 3, 200, 41, 77, 310]
+    result = subprocess.run([sys.executable, os.path.join(helpers.ROOT, "bin", "vipera"), "generate", path, "--prompt",
+                             " ".join(str(t) for t in prompt), "--max-tokens", "10"], capture_output=True, text=True,
+                            timeout=900)
+    assert result.returncode == 0, result.stderr[-2000:]
+    produced = [int(word) for word in result.stdout.split() if word.isdigit()][:10]
+    assert len(produced) == 10
+    logits = reference(path, prompt + produced[:-1], "bfloat16")
+    for index, token in enumerate(produced):
+        row = logits[len(prompt) - 1 + index]
+        assert float(row.max() - row[token]) <= 3e-2 * float(np.abs(row).max()), (index, token)
+    sampled = subprocess.run([sys.executable, os.path.join(helpers.ROOT, "bin", "vipera"), "generate", path, "--prompt",
+                              "5 17 3", "--max-tokens", "6", "--temperature", "0.8", "--seed", "7", "--top-k", "40"],
+                             capture_output=True, text=True, timeout=900)
+    assert sampled.returncode == 0 and len([w for w in sampled.stdout.split() if w.isdigit()]) >= 6
