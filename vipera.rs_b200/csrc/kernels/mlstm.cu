@@ -6,7 +6,7 @@
 //   m' = max(lf + m, li)
 //   S' = exp(lf + m - m') S + exp(li - m') k v^T,   n' likewise with k alone
 //   o  = S'^T q / (max(|n' . q|, exp(-m')) + denom_eps),  q scaled by q_scale
-// S, n and m start at `initial_max`-free zeros (m at 0) and live in 32-bit floats, one row per
+// S, n and m start at zero (m at 0, not at minus infinity) and live in 32-bit floats, one row per
 // state slot: [S: heads * d * dv | n: heads * d | m: heads].
 //
 // A chunk of L tokens is computed at once.  With b_t the sum of lf over the chunk's tokens up
@@ -14,8 +14,10 @@
 //   S_t^T q_t = exp(m_0 - M_t) S_0^T q_t + sum_{s<=t} exp(a_s - M_t) (q_t . k_s) v_s
 //   n_t . q_t = exp(m_0 - M_t) n_0 . q_t + sum_{s<=t} exp(a_s - M_t) (q_t . k_s)
 //   S_L = exp(m_0 - M_L) S_0 + sum_s exp(a_s - M_L) k_s v_s^T
-// Every exponent is at most 0.  All of it is 32-bit arithmetic on the CUDA cores; q, k, v and
-// the gates' pre-activations come from one product (the caller's) as 32-bit values.
+// Every exponent is at most 0.  q, k, v and the gates' pre-activations come from one product (the
+// caller's) as 32-bit values.  The first kernel below is that form in 32-bit arithmetic on the CUDA
+// cores (the 32-bit run, and sizes the others do not take); further down the same on the tensor
+// cores for bfloat16 runs, walking an entry's chunks or computing all chunks of a step at once.
 //
 // A block owns (value-column tile, head, entry) and walks the entry's tokens chunk by chunk with
 // its tile of S in shared memory.  n and m do not depend on the value columns: every tile
