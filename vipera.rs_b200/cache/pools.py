@@ -21,7 +21,7 @@ import torch
 
 from ..build import runtime_module
 from ..errors import InvalidArgumentError
-from ..parts.base import FixedState, PagedKV, PagedKVView, StateView
+from ..parts.base import FixedState, PagedKV, PagedKVView, StateView, bundle_views, flatten_cache_requests
 
 
 GUARD_WORD = 0x5A5A   # fits 16 bits: the guard regions are viewed as integers of the element's width
@@ -45,13 +45,12 @@ class CacheGroup:
 
 
 def plan_groups(cache_requests: Dict[int, object]) -> Tuple[List[CacheGroup], Dict[int, FixedState]]:
-    """Sort the cache slots of a model into paged groups and fixed-state slots."""
+    """Sort the cache slots of a model into paged groups and fixed-state slots.  A slot that keeps
+    several things (a ``CacheBundle``) appears once per member, under the key (slot, name)."""
     groups: Dict[tuple, CacheGroup] = {}
-    states: Dict[int, FixedState] = {}
-    for slot in sorted(cache_requests):
-        request = cache_requests[slot]
-        if request is None:
-            continue
+    states: Dict[object, FixedState] = {}
+    flat = flatten_cache_requests(cache_requests)
+    for slot, request in flat.items():
         if isinstance(request, PagedKV):
             value_dim = request.value_dim if request.value_dim and request.value_dim != request.head_dim else 0
             keep_first = int(request.keep_first or 0) if request.window else 0
@@ -89,7 +88,7 @@ class CachePools:
             # a mixer with a state of its own would have to store that state at every page's end
             bool(reuse_prefixes) and not self.states)
         self.pool_tensors: List[torch.Tensor] = []
-        self.views: Dict[int, object] = {}
+        views: Dict[object, object] = {}
         # One page beyond those the manager hands out, per group: the scratch page.  No request
         # ever holds it; tokens that pad a captured step to its size class write there.
         self.scratch_pages: List[int] = list(self.num_pages)
@@ -115,11 +114,15 @@ class CachePools:
                 k = pool[base:base + rows * group.head_dim].view(*page_shape, group.head_dim)
                 v = pool[base + rows * group.head_dim:base + rows * (group.head_dim + group.v_dim)].view(
                     *page_shape, group.v_dim)
-                self.views[slot] = PagedKVView(index, k, v, self.page_size, group.window, group.keep_first)
+                views[slot] = PagedKVView(index, k, v, self.page_size, group.window, group.keep_first)
         for slot, request in self.states.items():
             # one row beyond the requests' own: the spare row, for entries that pad a captured step
             data = torch.zeros((int(num_state_slots) + 1, *request.shape), dtype=request.dtype, device=device)
-            self.views[slot] = StateView(data)
+            views[slot] = StateView(data)
+        self._flat_views = views
+        # what each cache slot of the schedule is handed: a view, or for a bundle a dict of views
+        self.views: Dict[int, object] = {slot: bundle_views(request, slot, views)
+                                         for slot, request in cache_requests.items() if request is not None}
 
     def guards_intact(self) -> bool:
         """Whether the guard regions in front of and behind every pool still hold their word."""
@@ -139,7 +142,7 @@ class CachePools:
 
     def bytes(self) -> int:
         total = sum(p.numel() * p.element_size() for p in self.pool_tensors)
-        for view in self.views.values():
+        for view in self._flat_views.values():
             if isinstance(view, StateView):
                 total += view.data.numel() * view.data.element_size()
         return total

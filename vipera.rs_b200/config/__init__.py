@@ -20,6 +20,7 @@ from .registry import (
 from .spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 from .qwen2 import Qwen2Config, qwen2_model_spec
 from .nobupel import NobupelConfig, nobupel_model_spec
+from .gusolix import GusolixConfig, gusolix_model_spec
 
 
 def read_config_json(model_dir: str) -> Dict[str, Any]:
@@ -63,6 +64,6 @@ __all__ = [
     "ARCHITECTURES", "BLOCKS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITION_ENCODINGS",
     "Architecture", "Registry", "register_architecture",
     "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry",
-    "Qwen2Config", "qwen2_model_spec", "NobupelConfig", "nobupel_model_spec",
+    "Qwen2Config", "qwen2_model_spec", "NobupelConfig", "nobupel_model_spec", "GusolixConfig", "gusolix_model_spec",
     "read_config_json", "architecture_of", "load_config",
 ]

@@ -14,6 +14,8 @@
 // (`value_dim`); with a window, the first `keep_first` keys of a request stay visible to every
 // later query, at their true positions; and a sink, an extra key of score 0 without a value,
 // which adds exp(0 - max) to the softmax's denominator (p_j = e^{s_j} / (1 + sum e^{s_j})).
+// Instead of a window the mask may be one of chunks (`chunk`): position i sees j <= i with
+// floor(i / chunk) = floor(j / chunk).  `out_scale` multiplies the output.
 //
 // This kernel is the attention of the 32-bit path and takes every head size that is a
 // up to 256 (keys and values each; sizes that are not a multiple of 8 are read value by value), any number of heads and groups, any page size.
@@ -70,7 +72,7 @@ attention_kernel(const T* __restrict__ q, T* __restrict__ out, const T* __restri
                  const T* __restrict__ v_pool, const int* __restrict__ token_seq,
                  const int* __restrict__ positions, const int* __restrict__ block_table, int table_width,
                  int page_size, int num_heads, int num_kv_heads, int head_dim, int value_dim, float scale,
-                 int window, int keep_first, int sink) {
+                 int window, int keep_first, int sink, int chunk, float out_scale) {
   __shared__ float q_shared[kWarpsPerBlock][kMaxHeadDim];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
@@ -80,7 +82,8 @@ attention_kernel(const T* __restrict__ q, T* __restrict__ out, const T* __restri
   const int kv_head = h / group;
   const int position = positions[t];
   const int* table = block_table + static_cast<size_t>(token_seq[t]) * table_width;
-  const int first = window > 0 ? max(0, position - window + 1) : 0;
+  // a mask of chunks: a query sees the keys of its own chunk of `chunk` positions, counted from 0
+  const int first = chunk > 0 ? position / chunk * chunk : (window > 0 ? max(0, position - window + 1) : 0);
 
   const T* q_row = q + (static_cast<size_t>(t) * num_heads + h) * head_dim;
   float* qs = q_shared[warp];
@@ -139,7 +142,7 @@ attention_kernel(const T* __restrict__ q, T* __restrict__ out, const T* __restri
 #pragma unroll
     for (int i = 0; i < kMaxHeadDim / 32; ++i) acc[i] *= alpha;
   }
-  const float inverse = 1.0f / running_sum;
+  const float inverse = out_scale / running_sum;
   T* out_row = out + (static_cast<size_t>(t) * num_heads + h) * value_dim;
 #pragma unroll
   for (int i = 0; i < kMaxHeadDim / 32; ++i) {
@@ -158,8 +161,9 @@ VIPERA_API int vipera_attention(const void* q, void* out, int dtype, const void*
                                 const int* token_seq, const int* positions, const int* block_table,
                                 int table_width, int page_size, int num_tokens, int num_heads,
                                 int num_kv_heads, int head_dim, int value_dim, float scale, int window,
-                                int keep_first, int sink, void* stream) {
+                                int keep_first, int sink, int chunk, float out_scale, void* stream) {
   if (num_tokens <= 0) return VIPERA_OK;
+  if (chunk < 0 || (chunk > 0 && window > 0)) return VIPERA_BAD_ARGUMENT;
   if (head_dim <= 0 || head_dim > kMaxHeadDim) return VIPERA_BAD_SHAPE;
   if (value_dim <= 0 || value_dim > kMaxHeadDim || keep_first < 0) return VIPERA_BAD_SHAPE;
   if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads != 0) return VIPERA_BAD_SHAPE;
@@ -170,13 +174,13 @@ VIPERA_API int vipera_attention(const void* q, void* out, int dtype, const void*
     attention_kernel<float><<<grid, kWarpsPerBlock * 32, 0, s>>>(
         static_cast<const float*>(q), static_cast<float*>(out), static_cast<const float*>(k_pool),
         static_cast<const float*>(v_pool), token_seq, positions, block_table, table_width, page_size,
-        num_heads, num_kv_heads, head_dim, value_dim, scale, window, keep_first, sink);
+        num_heads, num_kv_heads, head_dim, value_dim, scale, window, keep_first, sink, chunk, out_scale);
   else if (dtype == VIPERA_BF16)
     attention_kernel<__nv_bfloat16><<<grid, kWarpsPerBlock * 32, 0, s>>>(
         static_cast<const __nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(out),
         static_cast<const __nv_bfloat16*>(k_pool), static_cast<const __nv_bfloat16*>(v_pool), token_seq,
         positions, block_table, table_width, page_size, num_heads, num_kv_heads, head_dim, value_dim, scale, window,
-        keep_first, sink);
+        keep_first, sink, chunk, out_scale);
   else
     return VIPERA_BAD_DTYPE;
   return vipera_launch_status();

@@ -1,0 +1,131 @@
+// Mamba's selective scan over a step's flattened tokens, with each request's state kept between
+// steps.  Per channel c and state index n, for every token of a request in order:
+//
+//   dt      = softplus(dt_pre[t, c])                       (dt_pre: the step-size product, bias included)
+//   S[c, n] = exp(dt * A[c, n]) * S[c, n] + dt * x[t, c] * B[t, n]
+//   y[t, c] = sum_n S[c, n] * C[t, n] + D[c] * x[t, c]
+//   out     = y * silu(z[t, c])
+//
+// A = -exp(A_log) is formed once when the model is built.  S lives in 32-bit floats,
+// [slots, channels, states], starts at zero for a new request and is carried from portion to
+// portion.  Everything here is 32-bit arithmetic; only `out` takes the run's type.
+//
+// A channel is shared by LANES adjacent lanes of a warp (a power of two), each holding NPL states
+// in registers; the sum over n is a shuffle reduction.  A block covers kScanThreads / LANES
+// channels of one entry and walks the entry's tokens in order.  The same kernel serves portions
+// and single tokens.
+#include "common.cuh"
+
+constexpr int kScanThreads = 128;
+
+struct ScanParams {
+  const float* x;        // [tokens, channels]   conv + silu output
+  const float* dt_pre;   // [tokens, channels]
+  const float* bc;       // [tokens, 2 * states]  B then C
+  const float* z;        // [tokens, z_stride]    the gate's pre-activation at column z_offset
+  long long z_stride;
+  int z_offset;
+  const float* a;        // [channels, states]    negative
+  const float* d;        // [channels]
+  float* state;          // [slots, channels * states]
+  const int* entry_starts;
+  const int* state_slots;
+  const int* fresh;
+  void* out;             // [tokens, channels]
+  int channels, states, num_entries, lanes;
+};
+
+template <typename TO, int NPL>
+__global__ void __launch_bounds__(kScanThreads) mamba_scan_kernel(const ScanParams p) {
+  pdl_launch_dependents();
+  const int lanes = p.lanes;
+  const int sub = threadIdx.x % lanes;                      // which share of the states
+  const int c = (blockIdx.x * kScanThreads + threadIdx.x) / lanes;
+  const bool live = c < p.channels;
+  const int entry = blockIdx.y;
+  float a[NPL], s[NPL];
+#pragma unroll
+  for (int j = 0; j < NPL; ++j) {
+    const int n = sub * NPL + j;
+    a[j] = (live && n < p.states) ? p.a[static_cast<size_t>(c) * p.states + n] : 0.0f;
+    s[j] = 0.0f;
+  }
+  const float skip = live ? p.d[c] : 0.0f;
+  pdl_wait();
+  const int first = p.entry_starts[entry], last = p.entry_starts[entry + 1];
+  if (last <= first) return;
+  float* state = p.state + static_cast<size_t>(p.state_slots[entry]) * p.channels * p.states;
+  if (live && !p.fresh[entry]) {
+#pragma unroll
+    for (int j = 0; j < NPL; ++j) {
+      const int n = sub * NPL + j;
+      if (n < p.states) s[j] = state[static_cast<size_t>(c) * p.states + n];
+    }
+  }
+  TO* out = static_cast<TO*>(p.out);
+  const int cc = live ? c : 0;
+  for (int t = first; t < last; ++t) {
+    const float pre = p.dt_pre[static_cast<size_t>(t) * p.channels + cc];
+    const float x = p.x[static_cast<size_t>(t) * p.channels + cc];
+    const float dt = pre > 20.0f ? pre : log1pf(expf(pre));
+    const float* b_row = p.bc + static_cast<size_t>(t) * 2 * p.states;
+    const float* c_row = b_row + p.states;
+    const float dtx = dt * x;
+    float y = 0.0f;
+#pragma unroll
+    for (int j = 0; j < NPL; ++j) {
+      const int n = sub * NPL + j;
+      if (n < p.states) {
+        s[j] = fmaf(expf(dt * a[j]), s[j], dtx * b_row[n]);
+        y = fmaf(s[j], c_row[n], y);
+      }
+    }
+    for (int offset = lanes >> 1; offset > 0; offset >>= 1) y += __shfl_xor_sync(0xffffffffu, y, offset);
+    if (live && sub == 0) {
+      const float gate = p.z[static_cast<size_t>(t) * p.z_stride + p.z_offset + c];
+      y = fmaf(skip, x, y);
+      out[static_cast<size_t>(t) * p.channels + c] = from_float<TO>(y * (gate / (1.0f + expf(-gate))));
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int j = 0; j < NPL; ++j) {
+      const int n = sub * NPL + j;
+      if (n < p.states) state[static_cast<size_t>(c) * p.states + n] = s[j];
+    }
+  }
+}
+
+// How the states of a channel are dealt to lanes: (lanes, states per lane).
+static void scan_shape(int states, int* lanes, int* per_lane) {
+  int l = 1;
+  while (l < 32 && (states + l - 1) / l > 4) l *= 2;
+  *lanes = l;
+  const int need = (states + l - 1) / l;
+  *per_lane = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : need <= 8 ? 8 : 16;
+}
+
+VIPERA_API int vipera_mamba_scan(const ScanParams* params, int out_dtype, void* stream) {
+  ScanParams p = *params;
+  if (p.num_entries <= 0) return VIPERA_OK;
+  if (p.channels <= 0 || p.states <= 0 || p.states > 512) return VIPERA_BAD_SHAPE;
+  if (!p.x || !p.dt_pre || !p.bc || !p.z || !p.a || !p.d || !p.state || !p.entry_starts || !p.state_slots ||
+      !p.fresh || !p.out)
+    return VIPERA_BAD_ARGUMENT;
+  int per_lane = 1;
+  scan_shape(p.states, &p.lanes, &per_lane);
+  const int channels_per_block = kScanThreads / p.lanes;
+  dim3 grid((p.channels + channels_per_block - 1) / channels_per_block, p.num_entries);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define SCAN_CASE(N)                                                                                     \
+  if (per_lane == N) {                                                                                   \
+    if (out_dtype == VIPERA_BF16) return vipera_launch(mamba_scan_kernel<__nv_bfloat16, N>, grid, kScanThreads, 0, s, p); \
+    if (out_dtype == VIPERA_F32) return vipera_launch(mamba_scan_kernel<float, N>, grid, kScanThreads, 0, s, p);          \
+    return VIPERA_BAD_DTYPE;                                                                             \
+  }
+  SCAN_CASE(1) SCAN_CASE(2) SCAN_CASE(4) SCAN_CASE(8) SCAN_CASE(16)
+#undef SCAN_CASE
+  return VIPERA_BAD_SHAPE;
+}
+
+VIPERA_API int vipera_mamba_scan_params_size() { return static_cast<int>(sizeof(ScanParams)); }

@@ -178,6 +178,108 @@ VIPERA_API int vipera_rope_cache_partial(const float* qkv, void* q_out, int dtyp
   return VIPERA_BAD_DTYPE;
 }
 
+// The form with a norm over whole rows in front: the q row (all heads together) and the k row are
+// each divided by their root mean square, sqrt(mean(x^2) + eps), and multiplied by a weight per
+// value (`q_norm`, `k_norm`; null: that row is left as it is) before the first `rot_dims` values of
+// each head turn.  `v_from_k` != 0: there is no value projection, the values are the keys as
+// projected (before norm and rotation), and the input row is [heads*d + kv_heads*d].  One block
+// per token; sums in 32-bit in a fixed order.
+template <typename T>
+__global__ void __launch_bounds__(256)
+qk_prepare_kernel(const float* __restrict__ qkv, T* __restrict__ q_out, int num_heads, int num_kv_heads,
+                  int head_dim, int value_dim, int rot_dims, const float* __restrict__ q_norm,
+                  const float* __restrict__ k_norm, float eps, int v_from_k, const int* __restrict__ positions,
+                  const float* __restrict__ cos_table, const float* __restrict__ sin_table, int style,
+                  T* __restrict__ k_pool, T* __restrict__ v_pool, const int* __restrict__ token_seq,
+                  const int* __restrict__ block_table, int table_width, int page_size, int write_cache) {
+  __shared__ float scratch[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int q_width = num_heads * head_dim, k_width = num_kv_heads * head_dim;
+  const int qk_width = q_width + k_width;
+  const int v_width = num_kv_heads * value_dim;
+  const float* row = qkv + static_cast<size_t>(t) * (qk_width + (v_from_k ? 0 : v_width));
+  float q_inverse = 1.0f, k_inverse = 1.0f;
+  if (q_norm) {
+    float sum = 0.0f;
+    for (int i = threadIdx.x; i < q_width; i += blockDim.x) sum = fmaf(row[i], row[i], sum);
+    q_inverse = 1.0f / sqrtf(block_sum(sum, scratch) / static_cast<float>(q_width) + eps);
+  }
+  if (k_norm) {
+    float sum = 0.0f;
+    for (int i = threadIdx.x; i < k_width; i += blockDim.x) sum = fmaf(row[q_width + i], row[q_width + i], sum);
+    k_inverse = 1.0f / sqrtf(block_sum(sum, scratch) / static_cast<float>(k_width) + eps);
+  }
+  const int position = positions[t];
+  T* k_row = nullptr;
+  T* v_row = nullptr;
+  if (write_cache) {
+    const int page = block_table[static_cast<size_t>(token_seq[t]) * table_width + position / page_size];
+    if (page >= 0) {
+      const size_t at = static_cast<size_t>(page) * page_size + position % page_size;
+      k_row = k_pool + at * num_kv_heads * head_dim;
+      v_row = v_pool + at * num_kv_heads * value_dim;
+    }
+  }
+  const int half = rot_dims >> 1;
+  const float* cos_row = cos_table ? cos_table + static_cast<size_t>(position) * half : nullptr;
+  const float* sin_row = sin_table ? sin_table + static_cast<size_t>(position) * half : nullptr;
+  for (int item = threadIdx.x; item < qk_width; item += blockDim.x) {
+    const int h = item / head_dim, e = item % head_dim;
+    const bool is_q = h < num_heads;
+    const float inverse = is_q ? q_inverse : k_inverse;
+    const float* gain = is_q ? q_norm : k_norm;
+    const int base = h * head_dim - (is_q ? 0 : q_width);   // index of the head's first value within its own row
+    const float* head = row + static_cast<size_t>(h) * head_dim;
+    auto normed = [&](int i) { return gain ? head[i] * inverse * gain[base + i] : head[i]; };
+    float value = normed(e);
+    if (style != ROPE_NONE && e < rot_dims) {
+      if (style == ROPE_INTERLEAVED) {
+        const int i = e >> 1;
+        const float a = normed(2 * i), b = normed(2 * i + 1), c = cos_row[i], s = sin_row[i];
+        value = (e & 1) ? a * s + b * c : a * c - b * s;
+      } else {
+        const int i = e < half ? e : e - half;
+        const float a = normed(i), b = normed(i + half), c = cos_row[i], s = sin_row[i];
+        value = e < half ? a * c - b * s : a * s + b * c;
+      }
+    }
+    if (is_q) q_out[(static_cast<size_t>(t) * num_heads + h) * head_dim + e] = from_float<T>(value);
+    else if (k_row) k_row[static_cast<size_t>(h - num_heads) * head_dim + e] = from_float<T>(value);
+  }
+  if (v_row) {
+    const float* values = row + (v_from_k ? q_width : qk_width);
+    for (int item = threadIdx.x; item < v_width; item += blockDim.x) v_row[item] = from_float<T>(values[item]);
+  }
+}
+
+VIPERA_API int vipera_qk_prepare(const float* qkv, void* q_out, int dtype, int num_tokens, int num_heads,
+                                 int num_kv_heads, int head_dim, int value_dim, int rot_dims, const float* q_norm,
+                                 const float* k_norm, float eps, int v_from_k, const int* positions,
+                                 const float* cos_table, const float* sin_table, int style, void* k_pool, void* v_pool,
+                                 const int* token_seq, const int* block_table, int table_width, int page_size,
+                                 int write_cache, void* stream) {
+  if (num_tokens <= 0) return VIPERA_OK;
+  if (head_dim <= 0 || value_dim <= 0 || num_heads <= 0 || num_kv_heads <= 0) return VIPERA_BAD_SHAPE;
+  if (rot_dims < 0 || (rot_dims & 1) || rot_dims > head_dim) return VIPERA_BAD_SHAPE;
+  if (v_from_k && value_dim != head_dim) return VIPERA_BAD_SHAPE;
+  if (style != ROPE_NONE && rot_dims > 0 && (!cos_table || !sin_table)) return VIPERA_BAD_ARGUMENT;
+  if (write_cache && (!k_pool || !v_pool || !token_seq || !block_table || page_size <= 0)) return VIPERA_BAD_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  dim3 grid(num_tokens);
+  if (dtype == VIPERA_F32)
+    return vipera_launch(qk_prepare_kernel<float>, grid, 256, 0, s, qkv, static_cast<float*>(q_out), num_heads,
+        num_kv_heads, head_dim, value_dim, rot_dims, q_norm, k_norm, eps, v_from_k, positions, cos_table, sin_table, style,
+        static_cast<float*>(k_pool), static_cast<float*>(v_pool), token_seq, block_table, table_width, page_size, write_cache);
+  if (dtype == VIPERA_BF16)
+    return vipera_launch(qk_prepare_kernel<__nv_bfloat16>, grid, 256, 0, s, qkv, static_cast<__nv_bfloat16*>(q_out),
+        num_heads, num_kv_heads, head_dim, value_dim, rot_dims, q_norm, k_norm, eps, v_from_k, positions, cos_table, sin_table,
+        style, static_cast<__nv_bfloat16*>(k_pool), static_cast<__nv_bfloat16*>(v_pool), token_seq, block_table,
+        table_width, page_size, write_cache);
+  return VIPERA_BAD_DTYPE;
+}
+
 VIPERA_API int vipera_rope_cache(const float* qkv, void* q_out, int dtype, int num_tokens, int num_heads,
                                  int num_kv_heads, int head_dim, const int* positions,
                                  const float* cos_table, const float* sin_table, int style, void* k_pool,

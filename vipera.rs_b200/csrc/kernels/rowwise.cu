@@ -180,4 +180,100 @@ VIPERA_API int vipera_rmsnorm(const float* x, const float* weight, const int* ro
   return VIPERA_BAD_DTYPE;
 }
 
+// ---------------------------------------------------------------------------------------
+// Layer norm over rows of a 32-bit stream: (x - mean) / sqrt(var + eps) * w + b, the variance
+// being the mean of the squared deviations (two passes over the row, which stays in registers
+// when it is short enough).  `rows` picks the rows as in RMSNorm.  ACC: the output is 32-bit
+// and the result is added to what it holds (a sublayer's normalised output joining the
+// residual stream).  A block per row.
+// ---------------------------------------------------------------------------------------
+template <typename TO, bool ACC>
+__global__ void __launch_bounds__(kNormThreads)
+layernorm_kernel(const float* __restrict__ x, const float* __restrict__ weight, const float* __restrict__ bias,
+                 const int* __restrict__ rows, TO* __restrict__ out, int hidden, float eps) {
+  __shared__ float scratch[32];
+  pdl_launch_dependents();
+  const int r = blockIdx.x;
+  const bool fits = hidden <= kNormThreads * kNormRegs;
+  float gain[kNormRegs], shift[kNormRegs];
+  if (fits) {
+#pragma unroll
+    for (int j = 0; j < kNormRegs; ++j) {
+      const int i = threadIdx.x + j * kNormThreads;
+      gain[j] = i < hidden ? weight[i] : 0.0f;
+      shift[j] = i < hidden ? bias[i] : 0.0f;
+    }
+  }
+  pdl_wait();
+  const int src_row = rows ? rows[r] : r;
+  const float* src = x + static_cast<size_t>(src_row) * hidden;
+  TO* dst = out + static_cast<size_t>(r) * hidden;
+  float kept[kNormRegs];
+  float sum = 0.0f;
+  if (fits) {
+#pragma unroll
+    for (int j = 0; j < kNormRegs; ++j) {
+      const int i = threadIdx.x + j * kNormThreads;
+      kept[j] = i < hidden ? src[i] : 0.0f;
+      sum += kept[j];
+    }
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += kNormThreads) sum += src[i];
+  }
+  const float mean = block_sum(sum, scratch) / static_cast<float>(hidden);
+  float squares = 0.0f;
+  if (fits) {
+#pragma unroll
+    for (int j = 0; j < kNormRegs; ++j) {
+      const int i = threadIdx.x + j * kNormThreads;
+      const float d = i < hidden ? kept[j] - mean : 0.0f;
+      squares += d * d;
+    }
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += kNormThreads) {
+      const float d = src[i] - mean;
+      squares += d * d;
+    }
+  }
+  const float inverse = 1.0f / sqrtf(block_sum(squares, scratch) / static_cast<float>(hidden) + eps);
+  if (fits) {
+#pragma unroll
+    for (int j = 0; j < kNormRegs; ++j) {
+      const int i = threadIdx.x + j * kNormThreads;
+      if (i < hidden) {
+        const float v = (kept[j] - mean) * inverse * gain[j] + shift[j];
+        if (ACC) dst[i] = from_float<TO>(to_float<TO>(dst[i]) + v);
+        else dst[i] = from_float<TO>(v);
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += kNormThreads) {
+      const float v = (src[i] - mean) * inverse * weight[i] + bias[i];
+      if (ACC) dst[i] = from_float<TO>(to_float<TO>(dst[i]) + v);
+      else dst[i] = from_float<TO>(v);
+    }
+  }
+}
+
+// accumulate != 0: out is 32-bit and receives out + norm(x).
+VIPERA_API int vipera_layernorm(const float* x, const float* weight, const float* bias, const int* rows, void* out,
+                                int out_dtype, int num_rows, int hidden, float eps, int accumulate, void* stream) {
+  if (num_rows <= 0) return VIPERA_OK;
+  if (hidden <= 0) return VIPERA_BAD_SHAPE;
+  if (!weight || !bias) return VIPERA_BAD_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (accumulate) {
+    if (out_dtype != VIPERA_F32) return VIPERA_BAD_DTYPE;
+    return vipera_launch(layernorm_kernel<float, true>, num_rows, kNormThreads, 0, s, x, weight, bias, rows,
+                         static_cast<float*>(out), hidden, eps);
+  }
+  if (out_dtype == VIPERA_F32)
+    return vipera_launch(layernorm_kernel<float, false>, num_rows, kNormThreads, 0, s, x, weight, bias, rows,
+                         static_cast<float*>(out), hidden, eps);
+  if (out_dtype == VIPERA_BF16)
+    return vipera_launch(layernorm_kernel<__nv_bfloat16, false>, num_rows, kNormThreads, 0, s, x, weight, bias, rows,
+                         static_cast<__nv_bfloat16*>(out), hidden, eps);
+  return VIPERA_BAD_DTYPE;
+}
+
 VIPERA_API const char* vipera_rowwise_status_text(int status) { return vipera_status_text(status); }

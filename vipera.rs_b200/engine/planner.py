@@ -15,6 +15,7 @@ from ..cache.pools import plan_groups
 from ..config.registry import BLOCKS
 from ..config.spec import ModelSpec
 from ..parts.model import model_schema
+from ..weights.loader import FREE_EXTENT
 
 DEVICE_RESERVE_BYTES = 16 << 20  # kept free on the device (crates/vipera-core/src/planner.rs:23)
 PLANNED_STEP_TOKENS = 2048       # the step the workspace is sized for
@@ -42,7 +43,7 @@ def weight_bytes(spec: ModelSpec, element_bytes: int) -> int:
     for tensor in model_schema(spec).values():
         count = 1
         for extent in tensor.shape:
-            count *= int(extent)
+            count *= FREE_EXTENT if extent is None else int(extent)
         total += count * (element_bytes if tensor.store == "model" else 4)
     return total
 
@@ -52,7 +53,7 @@ def parameter_count(spec: ModelSpec) -> int:
     for tensor in model_schema(spec).values():
         count = 1
         for extent in tensor.shape:
-            count *= int(extent)
+            count *= FREE_EXTENT if extent is None else int(extent)
         total += count
     return total
 

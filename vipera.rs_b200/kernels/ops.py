@@ -92,11 +92,12 @@ class KernelProfile:
         "embed": "embed", "rmsnorm": "norm", "rope_cache": "rope_kv",
         "gemm_tc": "proj", "gemm_tc_rope": "proj", "gemv_small": "proj", "gemm_simt": "proj",
         "attention": "attention", "attention_prefill": "attention", "attention_prefill_tc": "attention",
-        "attention_decode": "attention", "mlstm": "recurrence",
+        "attention_decode": "attention", "mlstm": "recurrence", "mamba_scan": "recurrence", "gla": "recurrence",
+        "layernorm": "norm", "causal_conv": "conv",
         "argmax": "sample", "sample": "sample", "apply_penalties": "sample", "feed_tokens": "sample",
         "logprobs": "sample",
     }
-    ORDER = ("proj", "attention", "recurrence", "norm", "rope_kv", "embed", "sample", "other")
+    ORDER = ("proj", "attention", "recurrence", "norm", "conv", "rope_kv", "embed", "sample", "other")
 
     def __init__(self):
         self._events = []
@@ -346,13 +347,18 @@ def _check_gemm_outputs(m, n, epilogue, bias, out, resid) -> None:
 def attention(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, *,
               token_seq: torch.Tensor, positions: torch.Tensor, block_table: torch.Tensor,
               num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: int = 0,
-              value_dim: Optional[int] = None, keep_first: int = 0, sink: bool = False) -> None:
+              value_dim: Optional[int] = None, keep_first: int = 0, sink: bool = False, chunk: int = 0,
+              out_scale: float = 1.0) -> None:
     """Causal grouped-query attention of every token of the step over its request's pages.
     ``value_dim``: a value row's size (default d); ``keep_first``: with a window, that many
-    first keys stay visible; ``sink``: one is added to the softmax's denominator."""
+    first keys stay visible; ``sink``: one is added to the softmax's denominator; ``chunk``:
+    instead of a window, a query sees the earlier keys of its own chunk of that many positions
+    (chunks counted from position 0); ``out_scale`` multiplies the output."""
     fn = _function("attention", "vipera_attention",
                    [_c_void, _c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int,
-                    _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_void])
+                    _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void])
+    if chunk and window:
+        raise InvalidArgumentError("attention: a mask is a window or chunks, not both")
     count = q.shape[0]
     value_dim = head_dim if value_dim is None else int(value_dim)
     for size in (head_dim, value_dim):
@@ -370,7 +376,8 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: 
               _gpu(token_seq, "token_seq", torch.int32), _gpu(positions, "positions", torch.int32),
               _gpu(block_table, "block_table", torch.int32), block_table.shape[1], page_size, count,
               num_heads, num_kv_heads, head_dim, value_dim, float(scale), int(window or 0),
-              int(keep_first or 0) if window else 0, 1 if sink else 0, _stream()), "attention")
+              int(keep_first or 0) if window else 0, 1 if sink else 0, int(chunk or 0), float(out_scale),
+              _stream()), "attention")
 
 
 # ----------------------------------------------------------------------------------------
@@ -984,3 +991,264 @@ def mlstm(proj: torch.Tensor, *, offsets, heads: int, dim: int, vdim: int, q_sca
 def kernel_status_word(device) -> torch.Tensor:
     """The device word in which kernels with bounded waits report that one ran out."""
     return _tc_buffers(device, 0)["status"]
+
+
+# ----------------------------------------------------------------------------------------
+# layer norm, short causal convolutions, norm over whole q/k rows
+# ----------------------------------------------------------------------------------------
+def layernorm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, out: torch.Tensor, eps: float,
+              rows: Optional[torch.Tensor] = None, accumulate: bool = False) -> None:
+    """out[r, :] = layernorm(x[rows[r], :]) * weight + bias; with ``accumulate`` the float32 ``out``
+    receives out + that instead (a normalised sublayer output joining the residual stream)."""
+    fn = _function("rowwise", "vipera_layernorm",
+                   [_c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void])
+    hidden = x.shape[1]
+    count = out.shape[0]
+    if out.shape[1] != hidden or weight.numel() != hidden or bias.numel() != hidden:
+        raise InvalidArgumentError("layernorm: widths of x, weight, bias and out do not agree")
+    if rows is None and x.shape[0] != count:
+        raise InvalidArgumentError("layernorm: x and out have different row counts")
+    if rows is not None and rows.numel() != count:
+        raise InvalidArgumentError("layernorm: one row index is needed for each output row")
+    if accumulate and (out.dtype != torch.float32 or out.data_ptr() == x.data_ptr()):
+        raise InvalidArgumentError("layernorm: accumulation needs a float32 target other than the input")
+    _check(fn(_gpu(x, "x", torch.float32), _gpu(weight, "weight", torch.float32), _gpu(bias, "bias", torch.float32),
+              _opt(rows, "rows", torch.int32), _gpu(out, "out"), dtype_code(out.dtype), count, hidden,
+              float(eps), 1 if accumulate else 0, _stream()), "layernorm")
+
+
+CONV_ACT_NONE, CONV_ACT_SILU = 0, 1
+CONV_ACTIVATIONS = {"none": CONV_ACT_NONE, "silu": CONV_ACT_SILU}
+CONV_MAX_TAPS = 8
+
+
+class _ConvParams(ctypes.Structure):
+    _fields_ = [
+        ("x", _c_void), ("x_stride", ctypes.c_longlong), ("weight", _c_void), ("bias", _c_void),
+        ("state", _c_void), ("state_stride", ctypes.c_longlong), ("entry_starts", _c_void), ("token_entry", _c_void),
+        ("state_slots", _c_void), ("fresh", _c_void), ("out", _c_void), ("out_f32", _c_void), ("clear", _c_void),
+        ("channels", _c_int), ("taps", _c_int), ("num_tokens", _c_int), ("num_entries", _c_int),
+        ("add_input", _c_int), ("activation", _c_int), ("segments", _c_int),
+    ]
+
+
+_struct_checked = set()
+
+
+def _check_struct(library: str, name: str, struct) -> None:
+    """The parameter block's size here and in the kernel file must agree."""
+    if (library, name) in _struct_checked:
+        return
+    size = _function(library, name, [])()
+    if size != ctypes.sizeof(struct):
+        raise InternalError(f"{library}: parameter block is {ctypes.sizeof(struct)} bytes here, {size} in the kernel")
+    _struct_checked.add((library, name))
+
+
+def causal_conv(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], *, channels: int,
+                state: Optional[torch.Tensor], entry_starts: torch.Tensor, token_entry: torch.Tensor,
+                state_slots: torch.Tensor, fresh: torch.Tensor, num_entries: int, single: bool,
+                add_input: bool, activation: int = CONV_ACT_NONE, out: Optional[torch.Tensor] = None,
+                out_f32: Optional[torch.Tensor] = None, clear: Optional[torch.Tensor] = None) -> None:
+    """A causal convolution over time per channel: ``y_t = act(sum_j w[:, j] x_(t - taps + 1 + j) + b)
+    (+ x_t)`` over the first ``channels`` columns of the float32 ``x`` [tokens, >= channels] (rows
+    may be strided).  ``state`` [slots, taps - 1, channels] float32 (slots may be strided) holds each
+    request's last inputs: read where an entry is not fresh, written at the entry's end.  ``out``
+    (any run type) and ``out_f32`` receive y; ``clear`` [tokens, channels] float32 is zeroed."""
+    fn = _function("seqconv", "vipera_causal_conv", [ctypes.POINTER(_ConvParams), _c_int, _c_int, _c_void])
+    _check_struct("seqconv", "vipera_causal_conv_params_size", _ConvParams)
+    tokens = x.shape[0]
+    taps = weight.shape[1]
+    if weight.shape[0] != channels or x.shape[1] < channels or x.stride(1) != 1 or x.dtype != torch.float32 or not x.is_cuda:
+        raise InvalidArgumentError("causal_conv: x must be float32 [tokens, >= channels] with unit inner stride")
+    if taps > CONV_MAX_TAPS:
+        raise UnsupportedError(f"causal_conv: {taps} taps; the kernel takes up to {CONV_MAX_TAPS}")
+    if out is None and out_f32 is None:
+        raise InvalidArgumentError("causal_conv: no output")
+    for name, tensor in (("out", out), ("out_f32", out_f32), ("clear", clear)):
+        if tensor is not None and tuple(tensor.shape) != (tokens, channels):
+            raise InvalidArgumentError(f"causal_conv: {name} must be [tokens, channels]")
+    p = _ConvParams()
+    p.x, p.x_stride = x.data_ptr(), x.stride(0)
+    p.weight, p.bias = _gpu(weight, "weight", torch.float32), _opt(bias, "bias", torch.float32)
+    if state is not None and taps > 1:
+        if tuple(state.shape[1:]) != (taps - 1, channels) or state.dtype != torch.float32 or \
+                state.stride(2) != 1 or state.stride(1) != channels:
+            raise InvalidArgumentError("causal_conv: state must be float32 [slots, taps - 1, channels]")
+        p.state, p.state_stride = state.data_ptr(), state.stride(0)
+    elif taps > 1:
+        raise InvalidArgumentError("causal_conv: a convolution of several taps needs its state")
+    p.entry_starts = _gpu(entry_starts, "entry_starts", torch.int32)
+    p.token_entry = _gpu(token_entry, "token_entry", torch.int32)
+    p.state_slots = _gpu(state_slots, "state_slots", torch.int32)
+    p.fresh = _gpu(fresh, "fresh", torch.int32)
+    p.out = _opt(out, "out")
+    p.out_f32 = _opt(out_f32, "out_f32", torch.float32)
+    p.clear = _opt(clear, "clear", torch.float32)
+    p.channels, p.taps, p.num_tokens, p.num_entries = int(channels), int(taps), int(tokens), int(num_entries)
+    p.add_input, p.activation = 1 if add_input else 0, int(activation)
+    _check(fn(ctypes.byref(p), dtype_code(out.dtype) if out is not None else F32, 1 if single else 0, _stream()),
+           "causal_conv")
+
+
+def qk_prepare(qkv: torch.Tensor, q_out: torch.Tensor, *, num_heads: int, num_kv_heads: int, head_dim: int,
+               value_dim: int, rot_dims: int, q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor],
+               eps: float, values_from_keys: bool, positions: torch.Tensor, cos: Optional[torch.Tensor],
+               sin: Optional[torch.Tensor], style: int, k_pool: torch.Tensor, v_pool: torch.Tensor,
+               token_seq: torch.Tensor, block_table: torch.Tensor, page_size: int, write_cache: bool) -> None:
+    """As ``rope_cache`` in its general form, with an RMS norm over the whole q row and the whole k
+    row (weights ``q_norm`` [heads * d], ``k_norm`` [kv_heads * d]) in front of the rotation, and,
+    with ``values_from_keys``, the keys as projected (before norm and rotation) stored as the values:
+    the float32 product is then [tokens, (heads + kv_heads) * d]."""
+    fn = _function("rope_cache", "vipera_qk_prepare",
+                   [_c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void, _c_float,
+                    _c_int, _c_void, _c_void, _c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int,
+                    _c_void])
+    count = qkv.shape[0]
+    width = (num_heads + num_kv_heads) * head_dim + (0 if values_from_keys else num_kv_heads * value_dim)
+    if qkv.shape[1] != width:
+        raise InvalidArgumentError("qk_prepare: the product's width does not match the head counts and sizes")
+    if tuple(q_out.shape) != (count, num_heads * head_dim):
+        raise InvalidArgumentError("qk_prepare: q_out has the wrong shape")
+    if style == ROPE_NONE:
+        rot_dims = 0
+    elif cos is None or sin is None or cos.shape[1] != rot_dims // 2 or sin.shape != cos.shape:
+        raise InvalidArgumentError("qk_prepare: cos/sin tables of width rot_dims/2 are needed")
+    if q_norm is not None and q_norm.numel() != num_heads * head_dim or \
+            k_norm is not None and k_norm.numel() != num_kv_heads * head_dim:
+        raise InvalidArgumentError("qk_prepare: a norm weight must have one value per value of its row")
+    if k_pool.dtype != q_out.dtype or v_pool.dtype != q_out.dtype or \
+            k_pool.shape[1:] != (page_size, num_kv_heads, head_dim) or \
+            v_pool.shape[1:] != (page_size, num_kv_heads, value_dim):
+        raise InvalidArgumentError("qk_prepare: cache pools must be [pages, page_size, kv_heads, d] and "
+                                   "[pages, page_size, kv_heads, value size] of the activation dtype")
+    _check(fn(_gpu(qkv, "qkv", torch.float32), _gpu(q_out, "q_out"), dtype_code(q_out.dtype), count, num_heads,
+              num_kv_heads, head_dim, value_dim, int(rot_dims), _opt(q_norm, "q_norm", torch.float32),
+              _opt(k_norm, "k_norm", torch.float32), float(eps), 1 if values_from_keys else 0,
+              _gpu(positions, "positions", torch.int32), _opt(cos, "cos", torch.float32), _opt(sin, "sin", torch.float32),
+              int(style), _gpu(k_pool, "k_pool"), _gpu(v_pool, "v_pool"), _gpu(token_seq, "token_seq", torch.int32),
+              _gpu(block_table, "block_table", torch.int32), block_table.shape[1], int(page_size),
+              1 if write_cache else 0, _stream()), "rope_cache")
+
+
+TALK_MAX_HEADS = 64
+
+
+def attention_talk(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, mix: torch.Tensor, *,
+                   token_seq: torch.Tensor, positions: torch.Tensor, block_table: torch.Tensor, num_heads: int,
+                   num_kv_heads: int, head_dim: int, value_dim: int, scale: float, out_scale: float = 1.0) -> None:
+    """Causal softmax attention whose normalised head weights are mixed by ``mix`` [heads, heads]
+    (``w_h = sum_g mix[h, g] p_g``) before head h applies them to the values of its own KV head."""
+    fn = _function("attention_talk", "vipera_attention_talk",
+                   [_c_void, _c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int,
+                    _c_int, _c_int, _c_int, _c_int, _c_float, _c_float, _c_void])
+    count = q.shape[0]
+    if num_heads > TALK_MAX_HEADS:
+        raise UnsupportedError(f"attention_talk: {num_heads} heads; the kernel takes up to {TALK_MAX_HEADS}")
+    if q.shape[1] != num_heads * head_dim or tuple(out.shape) != (count, num_heads * value_dim) or out.dtype != q.dtype:
+        raise InvalidArgumentError("attention_talk: q must be [tokens, heads * d] and out [tokens, heads * value size]")
+    page_size = k_pool.shape[1]
+    if k_pool.dtype != q.dtype or v_pool.dtype != q.dtype or k_pool.shape[2:] != (num_kv_heads, head_dim) or \
+            v_pool.shape[1:] != (page_size, num_kv_heads, value_dim):
+        raise InvalidArgumentError("attention_talk: cache pools do not match q and the head sizes")
+    if tuple(mix.shape) != (num_heads, num_heads):
+        raise InvalidArgumentError("attention_talk: the mixing matrix must be [heads, heads]")
+    _check(fn(_gpu(q, "q"), _gpu(out, "out"), dtype_code(q.dtype), _gpu(k_pool, "k_pool"), _gpu(v_pool, "v_pool"),
+              _gpu(mix, "mix", torch.float32), _gpu(token_seq, "token_seq", torch.int32),
+              _gpu(positions, "positions", torch.int32), _gpu(block_table, "block_table", torch.int32),
+              block_table.shape[1], page_size, count, num_heads, num_kv_heads, head_dim, value_dim, float(scale),
+              float(out_scale), _stream()), "attention")
+
+
+# ----------------------------------------------------------------------------------------
+# recurrences with a state of fixed size: Mamba's selective scan, gated linear attention
+# ----------------------------------------------------------------------------------------
+class _ScanParams(ctypes.Structure):
+    _fields_ = [
+        ("x", _c_void), ("dt_pre", _c_void), ("bc", _c_void), ("z", _c_void), ("z_stride", ctypes.c_longlong),
+        ("z_offset", _c_int), ("a", _c_void), ("d", _c_void), ("state", _c_void), ("entry_starts", _c_void),
+        ("state_slots", _c_void), ("fresh", _c_void), ("out", _c_void),
+        ("channels", _c_int), ("states", _c_int), ("num_entries", _c_int), ("lanes", _c_int),
+    ]
+
+
+def mamba_scan(x: torch.Tensor, dt_pre: torch.Tensor, bc: torch.Tensor, z: torch.Tensor, z_offset: int, *,
+               a: torch.Tensor, d: torch.Tensor, state: torch.Tensor, entry_starts: torch.Tensor,
+               state_slots: torch.Tensor, fresh: torch.Tensor, num_entries: int, out: torch.Tensor) -> None:
+    """Mamba's selective scan.  ``x`` (after convolution and silu) and ``dt_pre`` (the step-size
+    product with its bias, before softplus) are float32 [tokens, channels]; ``bc`` float32 [tokens,
+    2 * states] holds B then C; the gate's pre-activation is column ``z_offset + c`` of the float32
+    ``z``; ``a`` [channels, states] is -exp(A_log), ``d`` [channels]; ``state`` float32 [slots,
+    channels * states]; ``out`` [tokens, channels] receives y * silu(z)."""
+    fn = _function("mamba", "vipera_mamba_scan", [ctypes.POINTER(_ScanParams), _c_int, _c_void])
+    _check_struct("mamba", "vipera_mamba_scan_params_size", _ScanParams)
+    tokens, channels = x.shape
+    states = a.shape[1]
+    if tuple(dt_pre.shape) != (tokens, channels) or tuple(bc.shape) != (tokens, 2 * states) or \
+            tuple(out.shape) != (tokens, channels) or tuple(a.shape) != (channels, states) or d.numel() != channels:
+        raise InvalidArgumentError("mamba_scan: shapes do not agree")
+    if z.shape[0] != tokens or z.shape[1] < z_offset + channels or z.dtype != torch.float32 or not z.is_contiguous():
+        raise InvalidArgumentError("mamba_scan: the gate's rows are too short")
+    if state.dim() != 2 or state.shape[1] != channels * states:
+        raise InvalidArgumentError("mamba_scan: state rows must hold channels * states floats")
+    p = _ScanParams()
+    p.x, p.dt_pre, p.bc = _gpu(x, "x", torch.float32), _gpu(dt_pre, "dt_pre", torch.float32), _gpu(bc, "bc", torch.float32)
+    p.z, p.z_stride, p.z_offset = z.data_ptr(), z.shape[1], int(z_offset)
+    p.a, p.d = _gpu(a, "a", torch.float32), _gpu(d, "d", torch.float32)
+    p.state = _gpu(state, "state", torch.float32)
+    p.entry_starts = _gpu(entry_starts, "entry_starts", torch.int32)
+    p.state_slots = _gpu(state_slots, "state_slots", torch.int32)
+    p.fresh = _gpu(fresh, "fresh", torch.int32)
+    p.out = _gpu(out, "out")
+    p.channels, p.states, p.num_entries = int(channels), int(states), int(num_entries)
+    _check(fn(ctypes.byref(p), dtype_code(out.dtype), _stream()), "mamba_scan")
+
+
+class _GlaParams(ctypes.Structure):
+    _fields_ = [
+        ("proj", _c_void), ("proj_width", ctypes.c_longlong),
+        ("q_off", _c_int), ("k_off", _c_int), ("v_off", _c_int), ("g_off", _c_int),
+        ("z", _c_void), ("state", _c_void), ("entry_starts", _c_void), ("state_slots", _c_void), ("fresh", _c_void),
+        ("partial", _c_void), ("norm_weight", _c_void), ("out", _c_void),
+        ("heads", _c_int), ("dim", _c_int), ("vdim", _c_int), ("num_entries", _c_int), ("num_tokens", _c_int),
+        ("shares", _c_int), ("q_scale", _c_float), ("inv_tau", _c_float), ("eps", _c_float), ("out_scale", _c_float),
+    ]
+
+
+def gla_shares(dim: int) -> int:
+    """How many row shares of a head's state the scan kernel writes partial outputs for."""
+    fn = getattr(load_kernel_library("gla"), "vipera_gla_shares")
+    fn.argtypes, fn.restype = [_c_int], _c_int
+    return int(fn(int(dim)))
+
+
+def gla(proj: torch.Tensor, z: torch.Tensor, *, offsets, heads: int, dim: int, vdim: int, q_scale: float, tau: float,
+        norm_weight: torch.Tensor, norm_eps: float, out_scale: float, state: torch.Tensor, entry_starts: torch.Tensor,
+        state_slots: torch.Tensor, fresh: torch.Tensor, num_entries: int, partial: torch.Tensor, out: torch.Tensor) -> None:
+    """Gated linear attention over a step.  ``proj`` float32 [tokens, width] holds q, k, v and the
+    output gate's pre-activation at ``offsets``; ``z`` float32 [tokens, heads * dim] the decays'
+    pre-activations; ``state`` float32 [slots, heads * dim * vdim]; ``partial`` float32 scratch of
+    gla_shares(dim) * tokens * heads * vdim values; ``out`` [tokens, heads * vdim] receives the
+    normalised, gated and scaled output."""
+    fn = _function("gla", "vipera_gla", [ctypes.POINTER(_GlaParams), _c_int, _c_void])
+    _check_struct("gla", "vipera_gla_params_size", _GlaParams)
+    tokens = proj.shape[0]
+    if tuple(z.shape) != (tokens, heads * dim) or tuple(out.shape) != (tokens, heads * vdim):
+        raise InvalidArgumentError("gla: z must be [tokens, heads * d] and out [tokens, heads * value size]")
+    if state.dim() != 2 or state.shape[1] != heads * dim * vdim:
+        raise InvalidArgumentError("gla: state rows must hold heads * d * value size floats")
+    if partial.numel() < gla_shares(dim) * tokens * heads * vdim or norm_weight.numel() != vdim:
+        raise InvalidArgumentError("gla: the scratch is too small or the norm weight has the wrong size")
+    p = _GlaParams()
+    p.proj, p.proj_width = _gpu(proj, "proj", torch.float32), proj.shape[1]
+    p.q_off, p.k_off, p.v_off, p.g_off = (int(o) for o in offsets)
+    p.z, p.state = _gpu(z, "z", torch.float32), _gpu(state, "state", torch.float32)
+    p.entry_starts = _gpu(entry_starts, "entry_starts", torch.int32)
+    p.state_slots = _gpu(state_slots, "state_slots", torch.int32)
+    p.fresh = _gpu(fresh, "fresh", torch.int32)
+    p.partial = _gpu(partial, "partial", torch.float32)
+    p.norm_weight = _gpu(norm_weight, "norm_weight", torch.float32)
+    p.out = _gpu(out, "out")
+    p.heads, p.dim, p.vdim, p.num_entries, p.num_tokens = int(heads), int(dim), int(vdim), int(num_entries), int(tokens)
+    p.q_scale, p.inv_tau, p.eps, p.out_scale = float(q_scale), 1.0 / float(tau), float(norm_eps), float(out_scale)
+    _check(fn(ctypes.byref(p), dtype_code(out.dtype), _stream()), "gla", kernels=2)

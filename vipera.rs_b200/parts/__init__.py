@@ -1,7 +1,8 @@
 """Parts a decoder is put together from.  Importing this package registers the built-in
-kinds: ``rmsnorm``; ``rope_neox``, ``rope_interleaved`` and ``none``; ``gqa_attention`` and ``mlstm``; ``swiglu`` (also ``gated_mlp``); ``prenorm`` and ``prenorm_mixer``."""
-from . import attention, block, mlp, mlstm, norm, rotary  # noqa: F401  (registration)
+kinds: ``rmsnorm`` and ``layernorm``; ``rope_neox``, ``rope_interleaved`` and ``none``; ``gqa_attention``, ``mlstm``, ``mamba1``, ``gla`` and ``parallel``; ``swiglu`` (also ``gated_mlp``); ``prenorm``, ``prenorm_mixer`` and ``outnorm_conv``."""
+from . import attention, block, gla, mamba, mlp, mlstm, norm, parallel, rotary  # noqa: F401  (registration)
 from .base import (
+    CacheBundle,
     FeedForward,
     FixedState,
     Mixer,
@@ -19,6 +20,6 @@ from .linear import Linear, NormedInput, interleave_gate_up
 from .model import DecoderModel, model_schema
 
 __all__ = [
-    "FeedForward", "FixedState", "Mixer", "Norm", "PagedKV", "PagedKVView", "Part", "PositionEncoding",
+    "CacheBundle", "FeedForward", "FixedState", "Mixer", "Norm", "PagedKV", "PagedKVView", "Part", "PositionEncoding",
     "StateView", "StepContext", "Workspace", "Block", "Linear", "NormedInput", "interleave_gate_up", "DecoderModel", "model_schema",
 ]

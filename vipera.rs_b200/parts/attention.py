@@ -30,7 +30,14 @@ class GQAttention(Mixer):
     the first that many keys of a request stay visible to every later query, at their true
     positions) and ``sink`` (true: a key of score 0 without a value joins every softmax, which
     adds one to its denominator).  A position encoding may turn only the first values of a head
-    (its ``rot_dims``)."""
+    (its ``rot_dims``).  Further options: ``chunk`` (instead of a window, a mask of chunks: position
+    i sees j <= i with floor(i / chunk) = floor(j / chunk), chunks counted from a request's
+    position 0); ``values_from_keys`` (no value projection: the values are the keys as projected,
+    before norm and rotation); ``row_norm`` with ``norm_eps`` (the whole q row and the whole k row
+    are each divided by their root mean square and multiplied by a weight per value,
+    ``<q>.norm.weight`` and ``<k>.norm.weight``, before the rotation); ``talking_heads`` (the
+    softmax weights of the heads are mixed by ``<prefix>.talk.weight`` [heads, heads] before they
+    meet the values, ``w_h = sum_g M[h, g] p_g``); ``out_scale`` (multiplies the mixer's output)."""
 
     kernels = ("rope_cache", "attention", "attention_mma", "attention_tc")
     takes_lazy_input = True
@@ -52,6 +59,13 @@ class GQAttention(Mixer):
             f"{prefix}.{vn}.weight": TensorSpec((v_width, hidden)),
             f"{prefix}.{on}.weight": TensorSpec((hidden, params["num_heads"] * dv)),
         }
+        if params.get("values_from_keys", False):
+            del schema[f"{prefix}.{vn}.weight"]
+        if params.get("row_norm", False):
+            schema[f"{prefix}.{qn}.norm.weight"] = TensorSpec((q_width,), init="norm")
+            schema[f"{prefix}.{kn}.norm.weight"] = TensorSpec((kv_width,), init="norm")
+        if params.get("talking_heads", False):
+            schema[f"{prefix}.talk.weight"] = TensorSpec((params["num_heads"], params["num_heads"]), init="mix")
         if params.get("qkv_bias", False):
             schema[f"{prefix}.{qn}.bias"] = TensorSpec((q_width,), init="bias")
             schema[f"{prefix}.{kn}.bias"] = TensorSpec((kv_width,), init="bias")
@@ -75,7 +89,26 @@ class GQAttention(Mixer):
         if self.num_heads % self.num_kv_heads:
             raise UnsupportedError("the number of heads must be a multiple of the number of KV heads")
         qn, kn, vn, on = self._names(params)
-        fused = torch.cat([tensors[f"{prefix}.{n}.weight"] for n in (qn, kn, vn)], dim=0)
+        self.chunk = int(params.get("chunk") or 0)
+        self.values_from_keys = bool(params.get("values_from_keys", False))
+        self.row_norm = bool(params.get("row_norm", False))
+        self.norm_eps = float(params.get("norm_eps", 0.0))
+        self.out_scale = float(params.get("out_scale", 1.0))
+        self.talk = None
+        if self.chunk and self.window:
+            raise UnsupportedError("attention: a mask is a window or chunks, not both")
+        if self.values_from_keys and self.value_dim != self.head_dim:
+            raise UnsupportedError("attention: values that are the keys have the keys' size")
+        if params.get("talking_heads", False):
+            if self.window or self.chunk or self.sink:
+                raise UnsupportedError("attention: mixed head weights come with a plain causal mask only")
+            self.talk = tensors[f"{prefix}.talk.weight"].to(device=device, dtype=torch.float32).contiguous()
+        self.q_norm = self.k_norm = None
+        if self.row_norm:
+            self.q_norm = tensors[f"{prefix}.{qn}.norm.weight"].to(device=device, dtype=torch.float32).contiguous()
+            self.k_norm = tensors[f"{prefix}.{kn}.norm.weight"].to(device=device, dtype=torch.float32).contiguous()
+        fused = torch.cat([tensors[f"{prefix}.{n}.weight"] for n in ((qn, kn) if self.values_from_keys else (qn, kn, vn))],
+                          dim=0)
         bias = None
         if params.get("qkv_bias", False):
             bias = torch.cat([tensors[f"{prefix}.{n}.bias"].to(torch.float32) for n in (qn, kn, vn)], dim=0)
@@ -87,13 +120,18 @@ class GQAttention(Mixer):
         # The fused endings and the tensor-core attention kernels know the common form only: values as
         # long as keys, whole heads that turn, a plain window, a plain softmax.
         self.common_form = (self.value_dim == self.head_dim and self.rot_dims == self.head_dim
-                            and not self.keep_first and not self.sink and self.head_dim % 16 == 0)
+                            and not self.keep_first and not self.sink and self.head_dim % 16 == 0
+                            and not self.chunk and not self.values_from_keys and not self.row_norm
+                            and self.talk is None and self.out_scale == 1.0)
 
     def kernel_families(self):
         # the tensor-core attention kernels serve bfloat16 with head sizes 64 and 128; everything
         # else runs through the general kernel
         own = ["rope_cache", "attention"]
-        if self.dtype == torch.bfloat16 and self.head_dim in (64, 128) and self.value_dim == self.head_dim:
+        if self.talk is not None:
+            own.append("attention_talk")
+        plain_mask = not self.chunk and self.talk is None and self.out_scale == 1.0
+        if plain_mask and self.dtype == torch.bfloat16 and self.head_dim in (64, 128) and self.value_dim == self.head_dim:
             own.append("attention_mma")
             if self.head_dim in ops.TC_ATTENTION_HEAD_DIMS and not self.keep_first and not self.sink:
                 own.append("attention_tc")
@@ -158,8 +196,21 @@ class GQAttention(Mixer):
             self._attend(ctx, q, mixed, cache, table)
             self.out(ctx, mixed, epilogue=ops.EPI_RESIDUAL, resid=residual)
             return
-        qkv = ws.get("attention.qkv", (count, (heads + kv_heads) * d + kv_heads * dv), torch.float32)
+        qkv = ws.get("attention.qkv", (count, self.qkv.out_features), torch.float32)
         self.qkv(ctx, h, epilogue=ops.EPI_STORE, out=qkv)
+        if self.row_norm or self.values_from_keys:
+            if style is None:
+                raise UnsupportedError("attention: a norm over whole rows needs a position encoding of the rotary kind")
+            cos, sin = self.position.tables()
+            ops.qk_prepare(qkv, q, num_heads=heads, num_kv_heads=kv_heads, head_dim=d, value_dim=dv,
+                           rot_dims=self.rot_dims, q_norm=self.q_norm, k_norm=self.k_norm, eps=self.norm_eps,
+                           values_from_keys=self.values_from_keys, positions=ctx.positions, cos=cos, sin=sin,
+                           style=style, k_pool=cache.k, v_pool=cache.v, token_seq=ctx.token_entry,
+                           block_table=table, page_size=cache.page_size, write_cache=writes_cache)
+            mixed = ws.get("attention.out", (count, heads * dv), ctx.dtype)
+            self._attend(ctx, q, mixed, cache, table)
+            self.out(ctx, mixed, epilogue=ops.EPI_RESIDUAL, resid=residual)
+            return
         if style is None:
             # An encoding the fused kernel does not know: the part applies it to the 32-bit
             # product itself, then the kernel only converts and stores.
@@ -183,7 +234,13 @@ class GQAttention(Mixer):
         kernel otherwise; in every other case the general kernel."""
         heads, kv_heads, d = self.num_heads, self.num_kv_heads, self.head_dim
         window = self.window or 0
-        if ctx.dtype == torch.bfloat16 and d in ops.MMA_HEAD_DIMS and self.value_dim == d:
+        if self.talk is not None:
+            ops.attention_talk(q, mixed, cache.k, cache.v, self.talk, token_seq=ctx.token_entry,
+                               positions=ctx.positions, block_table=table, num_heads=heads, num_kv_heads=kv_heads,
+                               head_dim=d, value_dim=self.value_dim, scale=self.scale, out_scale=self.out_scale)
+            return
+        plain_mask = not self.chunk and self.out_scale == 1.0
+        if plain_mask and ctx.dtype == torch.bfloat16 and d in ops.MMA_HEAD_DIMS and self.value_dim == d:
             # Kept first keys and the sink are options of the mma.sync kernels (the flash kernel folds
             # the kept keys as tiles of their own, the split-key kernel as a split of its own); the
             # tcgen05 flash kernel serves attention without them.
@@ -220,7 +277,7 @@ class GQAttention(Mixer):
         ops.attention(q, mixed, cache.k, cache.v, token_seq=ctx.token_entry, positions=ctx.positions,
                       block_table=table, num_heads=heads, num_kv_heads=kv_heads, head_dim=d,
                       scale=self.scale, window=window, value_dim=self.value_dim, keep_first=self.keep_first,
-                      sink=self.sink)
+                      sink=self.sink, chunk=self.chunk, out_scale=self.out_scale)
 
 
 MIXERS.register("gqa_attention", GQAttention)

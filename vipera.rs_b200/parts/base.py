@@ -49,6 +49,51 @@ class FixedState:
     dtype: torch.dtype = torch.float32
 
 
+@dataclass(frozen=True)
+class CacheBundle:
+    """Several things kept between steps, under names: a layer whose mixer keeps pages and a
+    state beside them, or a state of several tensors.  ``members`` is a tuple of (name, request);
+    a member may be a bundle itself.  The part receives a dict name -> view in its place."""
+
+    members: Tuple[Tuple[str, Any], ...]
+
+    @staticmethod
+    def of(**members) -> Optional["CacheBundle"]:
+        """A bundle of the members that are not None; None when nothing is left."""
+        kept = tuple((name, request) for name, request in members.items() if request is not None)
+        return CacheBundle(kept) if kept else None
+
+
+def flatten_cache_requests(cache_requests: Dict[Any, Any]) -> Dict[Any, Any]:
+    """Bundles taken apart: a plain request keeps its slot as key, a member of a bundle gets
+    the key ``(slot, "name")`` (``"outer.inner"`` for a bundle within a bundle)."""
+    flat: Dict[Any, Any] = {}
+
+    def walk(slot, path, request):
+        if isinstance(request, CacheBundle):
+            for name, member in request.members:
+                walk(slot, f"{path}.{name}" if path else name, member)
+        elif request is not None:
+            flat[(slot, path) if path else slot] = request
+
+    for slot in sorted(cache_requests):
+        walk(slot, "", cache_requests[slot])
+    return flat
+
+
+def bundle_views(request, slot, flat_views: Dict[Any, Any]):
+    """The views of a request in the shape of the request: a view, or a dict name -> views."""
+
+    def build(path, item):
+        if isinstance(item, CacheBundle):
+            return {name: build(f"{path}.{name}" if path else name, member) for name, member in item.members}
+        if item is None:
+            return None
+        return flat_views[(slot, path) if path else slot]
+
+    return build("", request)
+
+
 class PagedKVView:
     """The pages of one cache slot: ``k`` is [pages, page_size, kv_heads, d] and ``v`` the same
     with the value size in the last place."""

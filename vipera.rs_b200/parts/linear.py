@@ -70,7 +70,10 @@ class Linear:
 
     kernels = ("gemm_simt",)
 
-    def __init__(self, weight: torch.Tensor, dtype: torch.dtype, device, bias: Optional[torch.Tensor] = None):
+    def __init__(self, weight: torch.Tensor, dtype: torch.dtype, device, bias: Optional[torch.Tensor] = None,
+                 min_tensor_core_inner: int = 0):
+        """``min_tensor_core_inner``: products with a smaller inner size run on the CUDA cores (for
+        the narrow second matrix of a low-rank pair, whose inner size is a fraction of a k-block)."""
         self.weight = weight.to(device=device, dtype=dtype).contiguous()
         self.bias = None if bias is None else bias.to(device=device, dtype=torch.float32).contiguous()
         self.out_features, self.in_features = self.weight.shape
@@ -78,6 +81,7 @@ class Linear:
         # The tcgen05 kernel reads the matrix by TMA: bfloat16, rows a multiple of 16 bytes long
         # and a 16-byte aligned base.  Other matrices run on the CUDA cores.
         self.tensor_core = (dtype == torch.bfloat16 and self.weight.shape[1] % 8 == 0
+                            and self.weight.shape[1] >= int(min_tensor_core_inner)
                             and self.weight.data_ptr() % 16 == 0)
 
     def kernel_families(self):

@@ -31,4 +31,33 @@ class RMSNorm(Norm):
         ops.rmsnorm(x, self.weight, out, self.eps, rows)
 
 
+class LayerNorm(Norm):
+    """``(x - mean) / sqrt(var + eps) * w + b`` with 32-bit statistics; the variance is the mean of
+    the squared deviations.  params: ``size``, ``eps``.  Tensors: ``<prefix>.weight`` and
+    ``<prefix>.bias`` [size].  ``add_into`` is the form a layer uses whose sublayer outputs are
+    normalised before they join the residual stream."""
+
+    kernels = ("rowwise",)
+
+    @classmethod
+    def schema(cls, params, prefix):
+        return {f"{prefix}.weight": TensorSpec((params["size"],), init="norm", store="float32"),
+                f"{prefix}.bias": TensorSpec((params["size"],), init="bias", store="float32")}
+
+    def __init__(self, params, prefix, tensors, dtype, device):
+        super().__init__(params, prefix, tensors, dtype, device)
+        self.size = int(params["size"])
+        self.eps = float(params["eps"])
+        self.weight = tensors[f"{prefix}.weight"].to(device=device, dtype=torch.float32).contiguous()
+        self.bias = tensors[f"{prefix}.bias"].to(device=device, dtype=torch.float32).contiguous()
+
+    def forward(self, ctx, x, out, rows=None):
+        ops.layernorm(x, self.weight, self.bias, out, self.eps, rows)
+
+    def add_into(self, ctx, x, residual):
+        """residual += norm(x), both 32-bit [tokens, size]."""
+        ops.layernorm(x, self.weight, self.bias, residual, self.eps, None, accumulate=True)
+
+
 NORMS.register("rmsnorm", RMSNorm)
+NORMS.register("layernorm", LayerNorm)

@@ -53,10 +53,28 @@ def yarn_blend(inverse: torch.Tensor, dims: int, theta: float, scaling: dict):
     return blended, 0.1 * math.log(factor) + 1.0
 
 
+def wavelength_blend(inverse: torch.Tensor, scaling: dict) -> torch.Tensor:
+    """Frequency scaling by wavelength, as Llama 3.1 does it.  With l = 2 pi / f a pair's wavelength:
+    f stays where l < original / high, becomes f / factor where l > original / low, and in between
+    is (1 - s) f / factor + s f with s = (original / l - low) / (high - low).  ``scaling`` holds
+    ``factor``, ``low``, ``high`` and ``original`` (the length the model first saw)."""
+    factor, original = float(scaling["factor"]), float(scaling["original"])
+    low, high = float(scaling["low"]), float(scaling["high"])
+    if not (factor > 0 and original > 0 and high > low):
+        raise InvalidArgumentError("wavelength scaling needs a positive factor and original, and high above low")
+    f = inverse.to(torch.float64)
+    wavelength = 2.0 * math.pi / f
+    s = (original / wavelength - low) / (high - low)
+    blended = (1.0 - s) * f / factor + s * f
+    out = torch.where(wavelength < original / high, f, torch.where(wavelength > original / low, f / factor, blended))
+    return out.to(torch.float32)
+
+
 def rotary_tables(head_dim: int, theta: float, max_positions: int, device, scaling=None) -> _Tables:
     """cos and sin, each float32 [max_positions, head_dim / 2], on ``device``; ``head_dim`` is the
-    count of values that turn.  ``scaling``: None, or the YaRN constants (see ``yarn_blend``)."""
-    frozen = None if not scaling else tuple(sorted((str(k), float(v)) for k, v in scaling.items()))
+    count of values that turn.  ``scaling``: None, the YaRN constants (see ``yarn_blend``), or with
+    ``kind = "llama3"`` the constants of ``wavelength_blend``."""
+    frozen = None if not scaling else tuple(sorted((str(k), str(v)) for k, v in scaling.items()))
     key = (head_dim, float(theta), max_positions, str(device), frozen)
     cached = _TABLES.get(key)
     if cached is not None:
@@ -66,7 +84,12 @@ def rotary_tables(head_dim: int, theta: float, max_positions: int, device, scali
     exponent = 2.0 * index / torch.tensor(float(head_dim), dtype=torch.float32)
     inverse = 1.0 / torch.pow(torch.tensor(float(theta), dtype=torch.float32), exponent)
     stretch = 1.0
-    if scaling:
+    if scaling and scaling.get("kind") == "llama3":
+        # this family's frequencies are formed in 64-bit and rounded once
+        exact = torch.pow(torch.tensor(float(theta), dtype=torch.float64),
+                          -2.0 * torch.arange(half, dtype=torch.float64) / float(head_dim))
+        inverse = wavelength_blend(exact, scaling)
+    elif scaling:
         inverse, stretch = yarn_blend(inverse, head_dim, float(theta), scaling)
     position = torch.arange(max_positions, dtype=torch.float32)
     angle = position[:, None] * inverse[None, :]

@@ -27,7 +27,18 @@ INIT = {
     "embedding": (0.0, 0.02),
     "bias": (0.0, 0.02),
     "norm": (1.0, 0.01),
+    "mix": (0.3, 0.4),        # a matrix that mixes heads
+    "filter": (0.0, 0.3),     # taps of a short convolution
+    "log_rate": (0.0, 0.5),   # logarithms of decay rates
 }
+
+# An extent a part leaves open (None in a TensorSpec's shape: the tensor's own shape decides)
+# takes this value in random-weights mode.
+FREE_EXTENT = 16
+
+
+def concrete_shape(shape) -> Tuple[int, ...]:
+    return tuple(FREE_EXTENT if extent is None else int(extent) for extent in shape)
 
 
 @dataclass(frozen=True)
@@ -158,10 +169,11 @@ class RandomSource(WeightSource):
         return list(self._schema)
 
     def shape(self, name: str) -> Tuple[int, ...]:
-        return self._schema[name].shape
+        return concrete_shape(self._schema[name].shape)
 
     def get(self, name: str) -> torch.Tensor:
         spec = self._schema[name]
+        spec = TensorSpec(concrete_shape(spec.shape), spec.init, spec.store)
         generator = torch.Generator(device=self._device)
         generator.manual_seed((self._seed * 0x9E3779B97F4A7C15 ^ _fnv1a64(name)) & 0x7FFFFFFFFFFFFFFF)
         if spec.store == "int32":
@@ -187,7 +199,8 @@ def check_source(schema: Schema, source: WeightSource) -> None:
     wrong = []
     for name in sorted(want & have):
         got = tuple(source.shape(name))
-        if got != tuple(schema[name].shape):
+        want_shape = tuple(schema[name].shape)
+        if len(got) != len(want_shape) or any(w is not None and w != g for w, g in zip(want_shape, got)):
             wrong.append(f"{name}: is {list(got)}, expected {list(schema[name].shape)}")
     if not (missing or unexpected or wrong):
         return
