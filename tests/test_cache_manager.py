@@ -276,9 +276,9 @@ def test_decode_step_inputs_are_filled_in_the_graphs_layout():
     total = 8 * bucket + 1 + bucket * sum(widths)
     buffer = np.full(total, -7, dtype=np.int32)
 
-    def fill(tokens, counts, pos0, fresh, rows, requests=(5, 9), vocab=100, limit=64):
+    def fill(tokens, counts, pos0, fresh, rows, requests=(5, 9), vocab=100, limit=64, pad_pages=()):
         return cache.fill_decode(list(requests), np.asarray(tokens, dtype=np.int32), counts, pos0, fresh, rows,
-                                 buffer.ctypes.data, bucket, widths, vocab, limit)
+                                 buffer.ctypes.data, bucket, widths, vocab, limit, list(pad_pages))
 
     assert fill([11, 22], [1, 1], [19, 2], [0, 1], [0, 1]) == 2
     b = bucket
@@ -295,6 +295,18 @@ def test_decode_step_inputs_are_filled_in_the_graphs_layout():
     second = buffer[8 * b + 1 + b * 2:].reshape(b, 4)
     assert second[0].tolist() == cache.table(5, 1).tolist() + [-1] and second[1].tolist() == cache.table(9, 1).tolist() + [-1] * 3
     assert second[2].tolist() == second[0].tolist()
+    # with a padding page per group the padding entries are tokens at position 0 on that page alone
+    assert fill([11, 22], [1, 1], [19, 2], [0, 1], [0, 1], pad_pages=(8, 8)) == 2
+    assert buffer[:b].tolist() == [11, 22, 11, 11]
+    assert buffer[b:2 * b].tolist() == [19, 2, 0, 0] and buffer[4 * b + 1:5 * b + 1].tolist() == [19, 2, 0, 0]
+    assert buffer[5 * b + 1:6 * b + 1].tolist() == [0, 1, 4, 4] and buffer[6 * b + 1:7 * b + 1].tolist() == [0, 1, 1, 1]
+    first = buffer[8 * b + 1:8 * b + 1 + b * 2].reshape(b, 2)
+    assert first[:2].tolist() == [cache.table(5, 0).tolist(), cache.table(9, 0).tolist() + [-1]]
+    assert first[2:].tolist() == [[8, -1]] * 2
+    second = buffer[8 * b + 1 + b * 2:].reshape(b, 4)
+    assert second[2:].tolist() == [[8, -1, -1, -1]] * 2
+    with pytest.raises(errors.InvalidArgumentError):
+        fill([11, 22], [1, 1], [19, 2], [0, 1], [0, 1], pad_pages=(8,))   # one page per group
     # not a plain decode step: a portion of two tokens, rows in another order, fewer rows than entries
     assert fill([1, 2, 3], [2, 1], [18, 2], [0, 0], [0, 1]) == -1
     assert fill([1, 2], [1, 1], [19, 2], [0, 0], [1, 0]) == -1

@@ -168,8 +168,15 @@ PYBIND11_MODULE(_vipera_runtime, m) {
            [](const CacheManager& c, const std::vector<int64_t>& requests, py::array_t<int32_t, py::array::c_style | py::array::forcecast> tokens,
               py::array_t<int32_t, py::array::c_style | py::array::forcecast> counts, py::array_t<int32_t, py::array::c_style | py::array::forcecast> pos0,
               py::array_t<int32_t, py::array::c_style | py::array::forcecast> fresh, py::array_t<int32_t, py::array::c_style | py::array::forcecast> rows,
-              uintptr_t host, int bucket, const std::vector<int>& widths, int vocab, int max_model_len) -> int {
+              uintptr_t host, int bucket, const std::vector<int>& widths, int vocab, int max_model_len,
+              const std::vector<int>& pad_pages) -> int {
+             // pad_pages: empty, or one page per group that no request holds.  Entries that pad the step
+             // are then tokens at position 0 whose block table names only that page, instead of copies
+             // of the first entry: where a model keeps state beside its pages, a copy on the spare state
+             // row would compute other keys and values than the entry it copies and store them in its place.
              const int n = static_cast<int>(requests.size());
+             if (!pad_pages.empty() && static_cast<int>(pad_pages.size()) != c.num_groups())
+               throw InvalidArgument("one padding page is needed for each group");
              if (n == 0 || n > bucket) throw InvalidArgument("a decode step needs between one entry and the graph's entry count");
              if (counts.size() != n || pos0.size() != n || fresh.size() != n)
                throw InvalidArgument("requests, counts and first positions must have one item per entry");
@@ -199,12 +206,13 @@ PYBIND11_MODULE(_vipera_runtime, m) {
              }
              for (size_t i = 0; i < b; ++i) {
                const int from = i < static_cast<size_t>(n) ? static_cast<int>(i) : 0;
-               out_tokens[i] = tok[from];
-               out_positions[i] = pos[from];
-               out_pos0[i] = pos[from];
                // an entry that pads the step works on the spare state row behind the requests' own,
                // from nothing, so that no request's state moves twice
                const bool own = i < static_cast<size_t>(n);
+               const bool elsewhere = !own && !pad_pages.empty();
+               out_tokens[i] = tok[from];
+               out_positions[i] = elsewhere ? 0 : pos[from];
+               out_pos0[i] = elsewhere ? 0 : pos[from];
                out_slots[i] = own ? c.state_slot(requests[from]) : c.num_state_slots();
                out_fresh[i] = own ? fr[from] : 1;
              }
@@ -219,6 +227,10 @@ PYBIND11_MODULE(_vipera_runtime, m) {
                  if (page >= static_cast<int>(table.size()) || table[page] < 0)
                    throw InvalidArgument("a request of the step has no page reserved for its position");
                  int32_t* dst = out_tables + i * width;
+                 if (i >= static_cast<size_t>(n) && !pad_pages.empty()) {
+                   for (int k = 0; k < width; ++k) dst[k] = k == 0 ? pad_pages[g] : -1;
+                   continue;
+                 }
                  for (int k = 0; k < width; ++k) dst[k] = k < static_cast<int>(table.size()) ? table[k] : -1;
                }
                out_tables += b * width;

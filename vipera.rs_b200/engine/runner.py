@@ -332,8 +332,9 @@ class ModelRunner:
 
 class _DecodeGraph:
     """One captured decode step for `bucket` entries and block tables of the given widths.
-    Steps with fewer entries are padded with copies of their first entry, which computes and
-    stores the same values twice."""
+    Steps with fewer entries are padded: with copies of their first entry, which computes and
+    stores the same values twice, or, where the model keeps state of fixed size, with tokens at
+    position 0 on the scratch page and the spare state row."""
 
     def __init__(self, runner: ModelRunner, bucket: int, widths):
         self._runner = weakref.ref(runner)   # the runner owns its graphs, not the other way round
@@ -351,6 +352,10 @@ class _DecodeGraph:
         view[int(o[3]):int(o[4])] = np.arange(b + 1, dtype=np.int32)
         view[int(o[7]):int(o[8])] = np.arange(b, dtype=np.int32)
         self.host_address = self.host.data_ptr()
+        # Where the model keeps state beside its pages, entries that pad the step are tokens at
+        # position 0 on each group's scratch page (on the spare state row they would compute other
+        # keys and values than the entry they copy, and store them in its place).
+        self.pad_pages = [int(page) for page in runner.pools.scratch_pages] if runner.pools.states else []
         self.vocab = int(runner.model.spec.vocab_size)
         self.copy_done = torch.cuda.Event()
         self.pending = False
@@ -379,7 +384,8 @@ class _DecodeGraph:
             self.copy_done.synchronize()
             self.pending = False
         n = runner.manager.fill_decode(step.requests, step.tokens, step.counts, step.pos0, step.fresh, step.logit_rows,
-                                       self.host_address, self.bucket, self.widths, self.vocab, runner.max_model_len)
+                                       self.host_address, self.bucket, self.widths, self.vocab, runner.max_model_len,
+                                       self.pad_pages)
         if n < 0:
             return n
         self.dev.copy_(self.host, non_blocking=True)
@@ -402,7 +408,7 @@ class _DecodeGraph:
             plain = self._plain[n] = (np.zeros(n, dtype=np.int32), np.ones(n, dtype=np.int32), np.arange(n, dtype=np.int32))
         zeros, ones, rows = plain
         runner.manager.fill_decode(requests, zeros, ones, pos0, zeros, rows, self.host_address, self.bucket, self.widths,
-                                   self.vocab, runner.max_model_len)
+                                   self.vocab, runner.max_model_len, self.pad_pages)
         self.dev.copy_(self.host, non_blocking=True)
         self.copy_done.record()
         self.pending = True
