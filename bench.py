@@ -550,6 +550,115 @@ def nobupel_decode_bytes(config, batch, history, element=2):
     return {"weights": weights * element, "state": state, "cache": cache}
 
 
+# ---------------------------------------------------------------------------------------
+# --design gusolix: the Gusolix design beside the Qwen2 decoder at equal sizes
+# ---------------------------------------------------------------------------------------
+def gusolix_config(width, heads, kv_heads, ff, layers, vocab, *_unused, chunk=1024):
+    """`layers` layers in the order attention, Mamba, and two layers of softmax attention with
+    mixed head weights beside gated linear attention; every layer with a feed-forward; heads of 128,
+    chunks of 1,024 keys, Mamba with twice the width in channels and 16 states."""
+    attention = {"type": "attention", "mlp": {"kind": "dense", "ff": ff},
+                 "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                           "mask": {"size": chunk},
+                           "rot": {"dims": 64, "base": 500000.0,
+                                   "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}}
+    mamba = {"type": "mamba1", "mlp": {"kind": "dense", "ff": ff},
+             "mixer": {"inner": 2 * width, "state": 16, "dt_rank": width // 16, "conv": 4}}
+    pair = {"type": "parallel", "mlp": {"kind": "dense", "ff": ff},
+            "mixer": {"left": {"heads": heads // 2, "kv_heads": max(kv_heads // 2, 1), "dim": 128, "vdim": 128,
+                               "scale": 128 ** -0.5},
+                      "right": {"heads": heads // 4, "dim": 128, "vdim": 256, "tau": 16.0, "rank": 16},
+                      "left_scale": 0.8, "right_scale": 0.9}}
+    order = (attention, mamba, pair, pair)
+    return {"architecture": "Gusolix", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "embedding": {"scale": float(width) ** 0.5}, "canon": {"taps": 4},
+            "layers": [order[index % 4] for index in range(layers)]}
+
+
+def gusolix_work(config, tokens):
+    """Floating-point operations of a prompt of `tokens` tokens by class of kernel: products,
+    attention within its mask (the mixed-weights form computes its scores twice), the
+    recurrences as their token-by-token forms compute them."""
+    width = config["width"]
+    flops = {"proj": 2.0 * config["vocab"] * width, "recurrence": 0.0, "attention": 0.0}
+
+    def softmax_heads(m, seen, passes):
+        flops["proj"] += 2.0 * tokens * width * (m["heads"] * m["dim"] + m["kv_heads"] * m["dim"] + m["heads"] * m["vdim"])
+        flops["attention"] += 2.0 * tokens * m["heads"] * (passes * m["dim"] + m["vdim"]) * seen
+
+    for layer in config["layers"]:
+        m = layer["mixer"]
+        if layer["type"] == "attention":
+            size = (m.get("mask") or {}).get("size") or tokens
+            softmax_heads(m, min(tokens, size) / 2, 1)
+        elif layer["type"] == "mamba1":
+            flops["proj"] += 2.0 * tokens * (width * 2 * m["inner"] + m["inner"] * (m["dt_rank"] + 2 * m["state"])
+                                             + m["dt_rank"] * m["inner"] + m["inner"] * width)
+            flops["recurrence"] += tokens * m["inner"] * m["state"] * 5.0
+        else:
+            left, right = m["left"], m["right"]
+            softmax_heads(left, tokens / 2, 2)
+            flops["proj"] += 2.0 * tokens * width * left["kv_heads"] * left["vdim"]
+            flops["attention"] += 2.0 * tokens * left["heads"] * left["heads"] * tokens / 2      # the mix of the weights
+            h, d, dv = right["heads"], right["dim"], right["vdim"]
+            flops["proj"] += 2.0 * tokens * (width * h * (2 * d + 3 * dv) + width * right["rank"] + right["rank"] * h * d)
+            flops["recurrence"] += tokens * h * d * dv * 4.0
+        if layer.get("mlp"):
+            flops["proj"] += 2.0 * tokens * 3 * width * layer["mlp"]["ff"]
+    return flops
+
+
+def gusolix_prefill_bytes(config, tokens):
+    """Bytes the recurrences of a prompt must move at least (their inputs once, their outputs once; the
+    state stays on the chip): the bound of kernels that do a handful of operations per value."""
+    moved = 0
+    for layer in config["layers"]:
+        m = layer["mixer"]
+        if layer["type"] == "mamba1":
+            moved += tokens * (m["inner"] * (4 + 4 + 4 + 2) + 2 * m["state"] * 4)       # x, dt, gate in 32-bit, out
+        elif layer["type"] == "parallel":
+            r = m["right"]
+            moved += tokens * r["heads"] * ((3 * r["dim"] + 2 * r["vdim"]) * 4 + r["vdim"] * 2)
+    return moved
+
+
+def gusolix_decode_bytes(config, batch, history, element=2):
+    width = config["width"]
+    weights = config["vocab"] * width
+    state = cache = 0
+    taps = config["canon"]["taps"]
+    for layer in config["layers"]:
+        m = layer["mixer"]
+        state += 2 * batch * 2 * (taps - 1) * width * 4
+        if layer["type"] == "attention":
+            weights += width * (m["heads"] * m["dim"] + m["kv_heads"] * m["dim"] + m["heads"] * m["vdim"])
+            size = (m.get("mask") or {}).get("size") or history
+            cache += batch * min(history, size / 2) * m["kv_heads"] * (m["dim"] + m["vdim"]) * element
+        elif layer["type"] == "mamba1":
+            weights += width * 2 * m["inner"] + m["inner"] * (m["dt_rank"] + 2 * m["state"]) + m["dt_rank"] * m["inner"] \
+                + m["inner"] * width
+            state += 2 * batch * m["inner"] * (m["state"] + m["conv"] - 1) * 4
+        else:
+            left, right = m["left"], m["right"]
+            weights += width * (left["heads"] * left["dim"] + left["kv_heads"] * (left["dim"] + left["vdim"])
+                                + left["heads"] * left["vdim"])
+            cache += batch * history * left["kv_heads"] * (left["dim"] + left["vdim"]) * element
+            h, d, dv = right["heads"], right["dim"], right["vdim"]
+            weights += width * h * (2 * d + 3 * dv) + width * right["rank"] + right["rank"] * h * d
+            state += 2 * batch * h * d * dv * 4
+        if layer.get("mlp"):
+            weights += 3 * width * layer["mlp"]["ff"]
+    return {"weights": weights * element, "state": state, "cache": int(cache)}
+
+
+DESIGNS = {
+    "nobupel": (lambda *sizes: nobupel_config(*sizes), lambda config, tokens: nobupel_work(config, tokens),
+                lambda config, batch, history: nobupel_decode_bytes(config, batch, history)),
+    "gusolix": (lambda *sizes: gusolix_config(*sizes), lambda config, tokens: gusolix_work(config, tokens),
+                lambda config, batch, history: gusolix_decode_bytes(config, batch, history)),
+}
+
+
 def profiled_prefill(model, tokens, page_size):
     """One prompt launched kernel by kernel with an event behind every launch: milliseconds by class of kernel."""
     from vipera_rs_b200.kernels import ops
@@ -585,7 +694,7 @@ def profiled_prefill(model, tokens, page_size):
 
 
 def measure_design(args, peaks, peak_source):
-    """Prefill and decode of Nobupel at sizes that resemble real layers, beside the Qwen2 decoder of
+    """Prefill and decode of the design at sizes that resemble real layers, beside the Qwen2 decoder of
     the same width, heads, inner size and layer count; random weights, bfloat16."""
     import torch  # noqa: F401
 
@@ -600,20 +709,25 @@ def measure_design(args, peaks, peak_source):
         if args.design_size and name != args.design_size:
             continue
         row = {}
-        for label, config in (("nobupel", nobupel_config(width, heads, kv_heads, ff, layers, vocab, cell_heads, cell_dim,
-                                                         cell_vdim)),
+        make_config, work_of, decode_bytes_of = DESIGNS[args.design]
+        for label, config in ((args.design, make_config(width, heads, kv_heads, ff, layers, vocab, cell_heads, cell_dim,
+                                                        cell_vdim)),
                               ("qwen2", qwen_like(width, heads, kv_heads, ff, layers, vocab))):
             model = random_model(config, seed=0, dtype="bfloat16", device="cuda:0")
             out = {"layers": layers}
             ms = measure_prefill(model, tokens, repeats=5, warmup=3, page_size=args.page_size)
             out["prefill_ms"], out["prefill_tok_s"] = round(ms, 3), round(tokens * 1000.0 / ms, 1)
             out["prefill_ms_by_class"] = profiled_prefill(model, tokens, args.page_size)
-            if label == "nobupel":
-                work = nobupel_work(config, tokens)
+            if label == args.design:
+                work = work_of(config, tokens)
                 out["prefill_flops_by_class"] = {k: round(v / 1e9, 2) for k, v in work.items()}
                 out["prefill_frac_by_class"] = {
                     k: round(v / (out["prefill_ms_by_class"][k] * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)
                     for k, v in work.items() if out["prefill_ms_by_class"].get(k)}
+                if args.design == "gusolix" and out["prefill_ms_by_class"].get("recurrence"):
+                    moved = gusolix_prefill_bytes(config, tokens)
+                    out["prefill_recurrence_hbm_frac"] = round(
+                        moved / (out["prefill_ms_by_class"]["recurrence"] * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
             else:
                 qc = dict(config, hidden_size=width)
                 out["prefill_frac"] = round(prefill_flops_head(qc, layers, tokens) / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)
@@ -624,8 +738,8 @@ def measure_design(args, peaks, peak_source):
                 del harness
                 release_memory()
                 out[f"decode_b{batch}_tok_s"], out[f"decode_b{batch}_ms"] = round(batch * 1000.0 / step_ms, 1), round(step_ms, 4)
-                if label == "nobupel":
-                    moved = nobupel_decode_bytes(config, batch, mean_history)
+                if label == args.design:
+                    moved = decode_bytes_of(config, batch, mean_history)
                     out[f"decode_b{batch}_hbm_frac"] = round(sum(moved.values()) / (step_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
                 else:
                     out[f"decode_b{batch}_hbm_frac"] = round(
@@ -634,7 +748,7 @@ def measure_design(args, peaks, peak_source):
             del model
             release_memory()
         sizes[name] = row
-    print(json.dumps({"design": "nobupel", "beside": "qwen2 at equal width, heads, inner size and layers",
+    print(json.dumps({"design": args.design, "beside": "qwen2 at equal width, heads, inner size and layers",
                       "dtype": "bf16", "data": "synthetic: seeded random weights, uniform random token ids",
                       "prefill_tokens": tokens, "history": args.history, "steps": args.steps, "warmup": warmup,
                       "peaks": peak_source, "sizes": sizes, "clocks": sampler.stop()}))
@@ -685,7 +799,7 @@ def main():
     parser.add_argument("--prefill-tokens", type=int, default=2048)
     parser.add_argument("--skip-workloads", action="store_true",
                         help="leave out the 7B mixed workload and the 32B shape")
-    parser.add_argument("--design", choices=["nobupel"], default=None,
+    parser.add_argument("--design", choices=sorted(DESIGNS), default=None,
                         help="instead of the headline: prefill and decode of that design at sizes that resemble "
                              "real layers, beside the Qwen2 decoder at equal sizes")
     parser.add_argument("--design-size", choices=sorted(DESIGN_SIZES), default=None, help="one of the sizes only")

@@ -141,7 +141,10 @@ class GusolixConfig:
             "right": {"heads": _integer(f"{where}.right.heads", right["heads"]),
                       "dim": _integer(f"{where}.right.dim", right["dim"]),
                       "vdim": _integer(f"{where}.right.vdim", right["vdim"]),
-                      "tau": _number(f"{where}.right.tau", right["tau"])},
+                      "tau": _number(f"{where}.right.tau", right["tau"]),
+                      # the inner size of the decay's two matrices; where config.json is silent the
+                      # stored tensors decide
+                      "rank": None if right.get("rank") is None else _integer(f"{where}.right.rank", right["rank"])},
             "left_scale": _number(f"{where}.left_scale", mixer["left_scale"], positive=False),
             "right_scale": _number(f"{where}.right_scale", mixer["right_scale"], positive=False),
         }
@@ -151,8 +154,9 @@ class GusolixConfig:
         layers = []
         for layer in self.layers:
             mixer = {k: v for k, v in layer.mixer.items() if v is not None}
-            if mixer.get("rot") is not None:
-                mixer["rot"] = {k: v for k, v in mixer["rot"].items() if v is not None}
+            for key in ("rot", "right"):
+                if isinstance(mixer.get(key), dict):
+                    mixer[key] = {k: v for k, v in mixer[key].items() if v is not None}
             layers.append({"type": layer.kind, "mixer": mixer,
                            "mlp": None if layer.ff is None else {"kind": "dense", "ff": layer.ff}})
         out: Dict[str, Any] = {"architecture": self.architecture, "vocab": self.vocab, "width": self.width,
@@ -194,7 +198,7 @@ def _parallel_part(config: GusolixConfig, m: Dict[str, Any]) -> PartSpec:
     linear = PartSpec("gla", {
         "hidden_size": config.width, "num_heads": right["heads"], "head_dim": right["dim"],
         "value_dim": right["vdim"], "tau": right["tau"], "norm_eps": config.eps,
-        "decay_rank": None,   # read from the tensor's shape
+        "decay_rank": right["rank"],
     })
     return PartSpec("parallel", {"branches": (("left", softmax, m["left_scale"]), ("right", linear, m["right_scale"]))})
 

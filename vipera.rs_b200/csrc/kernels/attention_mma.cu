@@ -20,6 +20,15 @@
 
 namespace {
 
+// The first key a query at `position` sees.  window > 0: the last `window` keys; window < 0: a
+// mask of chunks of -window positions counted from position 0 (the query sees the earlier keys
+// of its own chunk); 0: every earlier key.
+__device__ __forceinline__ int first_visible_key(int position, int window) {
+  if (window > 0) return max(0, position - window + 1);
+  if (window < 0) return position / (-window) * (-window);
+  return 0;
+}
+
 // ---------------------------------------------------------------------------------------
 // prefill / mixed: block = (tile of 64 queries of one entry, query head)
 // ---------------------------------------------------------------------------------------
@@ -80,7 +89,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
     }
   }
   const int last_pos = pos0 + tokens_here - 1;
-  const int first_key = window > 0 ? max(0, pos0 - window + 1) : 0;
+  const int first_key = first_visible_key(pos0, window);
   const int first_block = first_key / kKeys;
   const int end_key = last_pos + 1;
   // kept keys some row of the tile sees outside its window: those below the last row's window
@@ -113,7 +122,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
     const int row = q_warp * 16 + (lane >> 2) + r * 8;
     const int position = pos0 + row;
     row_limit[r] = row < tokens_here ? position : -1;  // rows past the end see nothing
-    row_first[r] = window > 0 ? max(0, position - window + 1) : 0;
+    row_first[r] = first_visible_key(position, window);
     kept_limit[r] = row < tokens_here ? min(keep_first, row_first[r]) - 1 : -1;   // kept keys the window does not hold
   }
   const float scale_log2 = scale * kLog2e;
@@ -198,7 +207,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int position = positions[entry];
   const int* table = block_table + static_cast<size_t>(entry) * table_width;
-  const int window_first = window > 0 ? max(0, position - window + 1) : 0;
+  const int window_first = first_visible_key(position, window);
   const bool kept_split = KEPT && split == num_splits;
   const int places = num_splits + ((KEPT && keep_first > 0) ? 1 : 0);
   // this split's visible keys are first_visible .. last_visible
@@ -368,7 +377,7 @@ __global__ void attention_combine_kernel(const float* __restrict__ partial_ml, c
   // only the splits that hold visible keys were written by the decode kernel
   const int position = positions[blockIdx.x];
   pdl_wait();
-  const int first_visible = window > 0 ? max(0, position - window + 1) : 0;
+  const int first_visible = first_visible_key(position, window);
   const int first = (first_visible / 32 * 32) / chunk;
   const int window_last = min(slices - 1, position / chunk);
   // the kept keys' split holds keys when the window has left some of them behind; it is folded in
@@ -461,7 +470,7 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, const __nv_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int position = positions[entry];
   const int* table = block_table + static_cast<size_t>(entry) * table_width;
-  const int first_visible = window > 0 ? max(0, position - window + 1) : 0;
+  const int first_visible = first_visible_key(position, window);
   // this block's share of the visible keys, in steps of 128
   const int first = first_visible / kKeys * kKeys;
   const int visible = position + 1 - first;

@@ -669,13 +669,20 @@ TC_ATTENTION_HEAD_DIMS = (64, 128)
 def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, *,
                       entry_starts: torch.Tensor, entry_pos0: torch.Tensor, block_table: torch.Tensor,
                       num_entries: int, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
-                      window: int = 0, skip_single: bool = False, keep_first: int = 0, sink: bool = False) -> None:
+                      window: int = 0, skip_single: bool = False, keep_first: int = 0, sink: bool = False,
+                      mask_chunk: int = 0) -> None:
     """Flash-style attention of a step whose entries bring any number of tokens (bfloat16,
     head sizes 64 and 128), on tcgen05 with accumulators in tensor memory
     (VIPERA_ATTENTION_TC=0 keeps it on the mma.sync kernel).
     ``skip_single`` leaves entries of one token out: attention_decode with ``entry_starts`` runs them.
     ``keep_first`` (with a window: that many first keys stay visible) and ``sink`` (one added to the
-    softmax's denominator) are served by the mma.sync kernel."""
+    softmax's denominator) are served by the mma.sync kernel, and so is ``mask_chunk`` (instead of
+    a window: a query sees the earlier keys of its own chunk of that many positions; the kernels
+    take it as a negative window)."""
+    if mask_chunk:
+        if window:
+            raise InvalidArgumentError("attention_prefill: a mask is a window or chunks, not both")
+        window = -int(mask_chunk)
     if head_dim not in MMA_HEAD_DIMS:
         raise UnsupportedError(f"attention_prefill: head size {head_dim} (built: 64, 128)")
     count = q.shape[0]
@@ -690,12 +697,12 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, 
              float(scale), int(window or 0))
     kinds = [_c_void] * 7 + [_c_int] * 7 + [_c_float, _c_int]
     skip = 1 if skip_single else 0
-    keep_first = int(keep_first or 0) if window else 0
+    keep_first = int(keep_first or 0) if window > 0 else 0
     if keep_first or sink:
         fn = _function("attention_mma", "vipera_attention_prefill_kept", kinds + [_c_int, _c_int, _c_int, _c_void])
         _check(fn(*pointers, *sizes, skip, keep_first, 1 if sink else 0, _stream()), "attention_prefill")
         return
-    if head_dim in TC_ATTENTION_HEAD_DIMS and os.environ.get("VIPERA_ATTENTION_TC", "1") != "0":
+    if head_dim in TC_ATTENTION_HEAD_DIMS and window >= 0 and os.environ.get("VIPERA_ATTENTION_TC", "1") != "0":
         fn = _function("attention_tc", "vipera_attention_prefill_tc", kinds + [_c_int, _c_int, _c_void, _c_void])
         _check(fn(*pointers, *sizes, k_pool.shape[0], skip, kernel_status_word(q.device).data_ptr(), _stream()),
                "attention_prefill_tc")
@@ -764,7 +771,7 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v
                      positions: torch.Tensor, block_table: torch.Tensor, num_heads: int, num_kv_heads: int,
                      head_dim: int, scale: float, window: int, chunk: int, num_splits: int,
                      scratch: torch.Tensor, entry_starts: Optional[torch.Tensor] = None, keep_first: int = 0,
-                     sink: bool = False) -> None:
+                     sink: bool = False, mask_chunk: int = 0) -> None:
     """Split-key attention of the entries that bring one token (bfloat16, head sizes 64 and
     128); the partial results of the splits are combined by a second kernel.  Without
     ``entry_starts`` every entry brings one token (q and out are [entries, heads * d], positions
@@ -772,7 +779,12 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v
     are [tokens, heads * d], ``positions`` holds each entry's first position, and entries of
     more than one token are skipped (attention_prefill with ``skip_single`` runs them).
     ``keep_first`` (with a window: that many first keys stay visible; they are one more split, so
-    the scratch is sized for ``num_splits + 1``) and ``sink`` (one added to the softmax's denominator)."""
+    the scratch is sized for ``num_splits + 1``) and ``sink`` (one added to the softmax's denominator).
+    ``mask_chunk``: instead of a window, chunks of that many positions (passed on as a negative window)."""
+    if mask_chunk:
+        if window:
+            raise InvalidArgumentError("attention_decode: a mask is a window or chunks, not both")
+        window = -int(mask_chunk)
     fn = _function("attention_mma", "vipera_attention_decode_kept",
                    [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int,
                     _c_int, _c_float, _c_int, _c_int, _c_int, _c_void, ctypes.c_size_t, _c_void, _c_int, _c_int, _c_void])
@@ -792,7 +804,7 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v
               _gpu(block_table, "block_table", torch.int32), block_table.shape[1], k_pool.shape[1], count,
               num_heads, num_kv_heads, head_dim, float(scale), int(window or 0), int(chunk), int(num_splits),
               _gpu(scratch, "scratch", torch.float32), scratch.numel(), _opt(entry_starts, "entry_starts", torch.int32),
-              int(keep_first or 0) if window else 0, 1 if sink else 0, _stream()), "attention_decode", kernels=2)
+              int(keep_first or 0) if window > 0 else 0, 1 if sink else 0, _stream()), "attention_decode", kernels=2)
 
 
 def attention_decode_scratch_floats(num_entries: int, num_heads: int, head_dim: int, num_splits: int) -> int:

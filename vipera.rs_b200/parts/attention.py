@@ -130,10 +130,10 @@ class GQAttention(Mixer):
         own = ["rope_cache", "attention"]
         if self.talk is not None:
             own.append("attention_talk")
-        plain_mask = not self.chunk and self.talk is None and self.out_scale == 1.0
+        plain_mask = self.talk is None and self.out_scale == 1.0
         if plain_mask and self.dtype == torch.bfloat16 and self.head_dim in (64, 128) and self.value_dim == self.head_dim:
             own.append("attention_mma")
-            if self.head_dim in ops.TC_ATTENTION_HEAD_DIMS and not self.keep_first and not self.sink:
+            if self.head_dim in ops.TC_ATTENTION_HEAD_DIMS and not self.keep_first and not self.sink and not self.chunk:
                 own.append("attention_tc")
         return tuple(dict.fromkeys(tuple(own) + self.qkv.kernel_families() + self.out.kernel_families()
                                    + self.position.kernel_families()))
@@ -239,12 +239,11 @@ class GQAttention(Mixer):
                                positions=ctx.positions, block_table=table, num_heads=heads, num_kv_heads=kv_heads,
                                head_dim=d, value_dim=self.value_dim, scale=self.scale, out_scale=self.out_scale)
             return
-        plain_mask = not self.chunk and self.out_scale == 1.0
-        if plain_mask and ctx.dtype == torch.bfloat16 and d in ops.MMA_HEAD_DIMS and self.value_dim == d:
+        if self.out_scale == 1.0 and ctx.dtype == torch.bfloat16 and d in ops.MMA_HEAD_DIMS and self.value_dim == d:
             # Kept first keys and the sink are options of the mma.sync kernels (the flash kernel folds
             # the kept keys as tiles of their own, the split-key kernel as a split of its own); the
             # tcgen05 flash kernel serves attention without them.
-            kept = dict(keep_first=self.keep_first, sink=self.sink)
+            kept = dict(keep_first=self.keep_first, sink=self.sink, mask_chunk=self.chunk)
             places = 1 if self.keep_first else 0
             if ctx.all_single:
                 chunk, splits = ops.decode_splits(ctx.num_entries, kv_heads, max(ctx.max_kv_len, 1),
