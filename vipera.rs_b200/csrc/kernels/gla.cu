@@ -16,6 +16,13 @@
 // walks the entry's tokens in order.  Each warp writes its share of o to a scratch
 // [row shares][tokens][heads*dv]; gla_finish_kernel adds the shares in a fixed order and applies
 // norm, gate and scale (a warp per (token, head)).
+//
+// Long steps are cut into chunks of kGlaChunk tokens that run side by side, in three launches:
+// every chunk from a zero state (its end state E and, per key channel, the sum of its log decays,
+// which gives the chunk's whole decay); per entry the states at the chunks' starts one after
+// another, S <- exp(sum log alpha) S + E, which also leaves the request's new state; every chunk
+// again from its start state, now with outputs.  The recurrence is linear in S, so this only
+// re-associates 32-bit sums.  Chunks are counted from where an entry's tokens start in the step.
 #include "common.cuh"
 
 constexpr int kGlaMaxShares = 16;
@@ -34,24 +41,59 @@ struct GlaParams {
   void* out;              // [tokens, heads * vdim]
   int heads, dim, vdim, num_entries, num_tokens, shares;
   float q_scale, inv_tau, eps, out_scale;
+  // the chunked form: mode 0 walks whole entries; 1 runs chunks from zero; 3 runs them from their start states
+  int mode, num_jobs;
+  float* chunk_state;     // [jobs, heads * dim * vdim]  end states (mode 1), then start states (mode 3)
+  float* chunk_decay;     // [jobs, heads * dim]         sums of the chunks' log decays
 };
+
+constexpr int kGlaChunk = 64;
+
+__device__ __forceinline__ bool gla_job(const int* __restrict__ entry_starts, int num_entries, int job, int* entry,
+                                        int* first, int* last) {
+  int before = 0;
+  for (int e = 0; e < num_entries; ++e) {
+    const int begin = entry_starts[e], count = entry_starts[e + 1] - begin;
+    const int chunks = (count + kGlaChunk - 1) / kGlaChunk;
+    if (job < before + chunks) {
+      *entry = e;
+      *first = begin + (job - before) * kGlaChunk;
+      *last = min(*first + kGlaChunk, begin + count);
+      return true;
+    }
+    before += chunks;
+  }
+  return false;
+}
 
 template <int ROWS>
 __global__ void __launch_bounds__(kGlaMaxShares * 32) gla_scan_kernel(const GlaParams p) {
   pdl_launch_dependents();
   const int lane = threadIdx.x & 31, share = threadIdx.x >> 5;
   const int column = blockIdx.x * 32 + lane;
-  const int head = blockIdx.y, entry = blockIdx.z;
+  const int head = blockIdx.y;
+  int entry = blockIdx.z;
   const bool live = column < p.vdim;
   const int row0 = share * ROWS;
-  float s[ROWS];
+  float s[ROWS], log_decay[ROWS];
 #pragma unroll
-  for (int r = 0; r < ROWS; ++r) s[r] = 0.0f;
+  for (int r = 0; r < ROWS; ++r) s[r] = log_decay[r] = 0.0f;
   pdl_wait();
-  const int first = p.entry_starts[entry], last = p.entry_starts[entry + 1];
-  if (last <= first) return;
-  float* state = p.state + (static_cast<size_t>(p.state_slots[entry]) * p.heads + head) * p.dim * p.vdim;
-  if (live && !p.fresh[entry]) {
+  int first, last;
+  float* state;
+  bool resume;
+  if (p.mode == 0) {
+    first = p.entry_starts[entry];
+    last = p.entry_starts[entry + 1];
+    if (last <= first) return;
+    state = p.state + (static_cast<size_t>(p.state_slots[entry]) * p.heads + head) * p.dim * p.vdim;
+    resume = !p.fresh[entry];
+  } else {
+    if (!gla_job(p.entry_starts, p.num_entries, blockIdx.z, &entry, &first, &last)) return;
+    state = p.chunk_state + (static_cast<size_t>(blockIdx.z) * p.heads + head) * p.dim * p.vdim;
+    resume = p.mode == 3;
+  }
+  if (live && resume) {
 #pragma unroll
     for (int r = 0; r < ROWS; ++r)
       if (row0 + r < p.dim) s[r] = state[static_cast<size_t>(row0 + r) * p.vdim + column];
@@ -70,18 +112,51 @@ __global__ void __launch_bounds__(kGlaMaxShares * 32) gla_scan_kernel(const GlaP
       if (row0 + r < p.dim) {
         // log sigmoid(z) = min(z, 0) - log1p(exp(-|z|))
         const float zz = z[r];
-        const float alpha = expf((fminf(zz, 0.0f) - log1pf(expf(-fabsf(zz)))) * p.inv_tau);
-        s[r] = fmaf(alpha, s[r], k[r] * v);
+        const float log_alpha = (fminf(zz, 0.0f) - log1pf(expf(-fabsf(zz)))) * p.inv_tau;
+        log_decay[r] += log_alpha;
+        s[r] = fmaf(expf(log_alpha), s[r], k[r] * v);
         o = fmaf(s[r], q[r] * p.q_scale, o);
       }
     }
-    if (live) partial[static_cast<size_t>(t) * out_width + column] = o;
+    if (live && p.mode != 1) partial[static_cast<size_t>(t) * out_width + column] = o;
   }
-  if (live) {
+  if (live && p.mode != 3) {
 #pragma unroll
     for (int r = 0; r < ROWS; ++r)
       if (row0 + r < p.dim) state[static_cast<size_t>(row0 + r) * p.vdim + column] = s[r];
   }
+  if (p.mode == 1 && blockIdx.x == 0 && lane == 0) {
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r)
+      if (row0 + r < p.dim)
+        p.chunk_decay[(static_cast<size_t>(blockIdx.z) * p.heads + head) * p.dim + row0 + r] = log_decay[r];
+  }
+}
+
+// Between the two chunk passes: per entry and state element, the states at the chunks' starts one
+// after another (they take the end states' places), and the request's new state.
+__global__ void __launch_bounds__(256) gla_chunk_starts_kernel(const GlaParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t width = static_cast<size_t>(p.heads) * p.dim * p.vdim;
+  const size_t item = static_cast<size_t>(blockIdx.x) * 256 + threadIdx.x;
+  const int entry = blockIdx.y;
+  if (item >= width) return;
+  const int begin = p.entry_starts[entry], count = p.entry_starts[entry + 1] - begin;
+  if (count <= 0) return;
+  int job = 0;
+  for (int e = 0; e < entry; ++e) job += (p.entry_starts[e + 1] - p.entry_starts[e] + kGlaChunk - 1) / kGlaChunk;
+  const int chunks = (count + kGlaChunk - 1) / kGlaChunk;
+  const size_t row = item / p.vdim;   // head * dim + key channel
+  float* state = p.state + static_cast<size_t>(p.state_slots[entry]) * width + item;
+  float s = p.fresh[entry] ? 0.0f : *state;
+  for (int k = 0; k < chunks; ++k, ++job) {
+    float* cell = p.chunk_state + static_cast<size_t>(job) * width + item;
+    const float end_state = *cell;
+    *cell = s;
+    s = fmaf(expf(p.chunk_decay[static_cast<size_t>(job) * p.heads * p.dim + row]), s, end_state);
+  }
+  *state = s;
 }
 
 template <typename TO>
@@ -125,11 +200,24 @@ VIPERA_API int vipera_gla(const GlaParams* params, int out_dtype, void* stream) 
   p.shares = (p.dim + rows - 1) / rows;
   if (p.shares > kGlaMaxShares) return VIPERA_BAD_SHAPE;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  dim3 grid((p.vdim + 31) / 32, p.heads, p.num_entries);
+  const bool chunked = p.num_jobs > 0 && p.chunk_state && p.chunk_decay;
+  auto pass = [&](int mode) -> int {
+    p.mode = mode;
+    dim3 grid((p.vdim + 31) / 32, p.heads, mode == 0 ? p.num_entries : p.num_jobs);
+    if (rows == 8) return vipera_launch(gla_scan_kernel<8>, grid, p.shares * 32, 0, s, p);
+    if (rows == 16) return vipera_launch(gla_scan_kernel<16>, grid, p.shares * 32, 0, s, p);
+    return vipera_launch(gla_scan_kernel<32>, grid, p.shares * 32, 0, s, p);
+  };
   int status;
-  if (rows == 8) status = vipera_launch(gla_scan_kernel<8>, grid, p.shares * 32, 0, s, p);
-  else if (rows == 16) status = vipera_launch(gla_scan_kernel<16>, grid, p.shares * 32, 0, s, p);
-  else status = vipera_launch(gla_scan_kernel<32>, grid, p.shares * 32, 0, s, p);
+  if (!chunked) status = pass(0);
+  else {
+    status = pass(1);
+    if (!status) {
+      const size_t width = static_cast<size_t>(p.heads) * p.dim * p.vdim;
+      status = vipera_launch(gla_chunk_starts_kernel, dim3(static_cast<unsigned>((width + 255) / 256), p.num_entries), 256, 0, s, p);
+    }
+    if (!status) status = pass(3);
+  }
   if (status) return status;
   const int items = p.num_tokens * p.heads;
   if (out_dtype == VIPERA_BF16) return vipera_launch(gla_finish_kernel<__nv_bfloat16>, (items + 3) / 4, 128, 0, s, p);

@@ -14,6 +14,13 @@
 // in registers; the sum over n is a shuffle reduction.  A block covers kScanThreads / LANES
 // channels of one entry and walks the entry's tokens in order.  The same kernel serves portions
 // and single tokens.
+//
+// Long steps are cut into chunks of kScanChunk tokens that run side by side, in three launches:
+// every chunk from a zero state (its end state E and the sum of its step sizes, which gives the
+// chunk's whole decay exp(A * sum dt)); per entry the states at the chunks' starts, one after
+// another, S <- exp(A * sum dt) * S + E, which also leaves the request's new state; every chunk
+// again from its start state, now with outputs.  The recurrence is linear in S, so this only
+// re-associates 32-bit sums.  Chunks are counted from where an entry's tokens start in the step.
 #include "common.cuh"
 
 constexpr int kScanThreads = 128;
@@ -33,7 +40,31 @@ struct ScanParams {
   const int* fresh;
   void* out;             // [tokens, channels]
   int channels, states, num_entries, lanes;
+  // the chunked form: mode 0 walks whole entries; 1 runs chunks from zero; 3 runs them from their start states
+  int mode, num_jobs;
+  float* chunk_state;    // [jobs, channels * states]  end states (mode 1), then start states (mode 3)
+  float* chunk_dt;       // [jobs, channels]           sums of the chunks' step sizes
 };
+
+constexpr int kScanChunk = 64;
+
+// Which (entry, first token, end) is job `job`: the entries' chunks are numbered one entry after another.
+__device__ __forceinline__ bool scan_job(const int* __restrict__ entry_starts, int num_entries, int job, int* entry,
+                                         int* first, int* last) {
+  int before = 0;
+  for (int e = 0; e < num_entries; ++e) {
+    const int begin = entry_starts[e], count = entry_starts[e + 1] - begin;
+    const int chunks = (count + kScanChunk - 1) / kScanChunk;
+    if (job < before + chunks) {
+      *entry = e;
+      *first = begin + (job - before) * kScanChunk;
+      *last = min(*first + kScanChunk, begin + count);
+      return true;
+    }
+    before += chunks;
+  }
+  return false;
+}
 
 template <typename TO, int NPL>
 __global__ void __launch_bounds__(kScanThreads) mamba_scan_kernel(const ScanParams p) {
@@ -42,7 +73,7 @@ __global__ void __launch_bounds__(kScanThreads) mamba_scan_kernel(const ScanPara
   const int sub = threadIdx.x % lanes;                      // which share of the states
   const int c = (blockIdx.x * kScanThreads + threadIdx.x) / lanes;
   const bool live = c < p.channels;
-  const int entry = blockIdx.y;
+  int entry = blockIdx.y;
   float a[NPL], s[NPL];
 #pragma unroll
   for (int j = 0; j < NPL; ++j) {
@@ -52,10 +83,21 @@ __global__ void __launch_bounds__(kScanThreads) mamba_scan_kernel(const ScanPara
   }
   const float skip = live ? p.d[c] : 0.0f;
   pdl_wait();
-  const int first = p.entry_starts[entry], last = p.entry_starts[entry + 1];
-  if (last <= first) return;
-  float* state = p.state + static_cast<size_t>(p.state_slots[entry]) * p.channels * p.states;
-  if (live && !p.fresh[entry]) {
+  int first, last;
+  float* state;
+  bool resume;
+  if (p.mode == 0) {
+    first = p.entry_starts[entry];
+    last = p.entry_starts[entry + 1];
+    if (last <= first) return;
+    state = p.state + static_cast<size_t>(p.state_slots[entry]) * p.channels * p.states;
+    resume = !p.fresh[entry];
+  } else {
+    if (!scan_job(p.entry_starts, p.num_entries, blockIdx.y, &entry, &first, &last)) return;
+    state = p.chunk_state + static_cast<size_t>(blockIdx.y) * p.channels * p.states;
+    resume = p.mode == 3;
+  }
+  if (live && resume) {
 #pragma unroll
     for (int j = 0; j < NPL; ++j) {
       const int n = sub * NPL + j;
@@ -64,6 +106,7 @@ __global__ void __launch_bounds__(kScanThreads) mamba_scan_kernel(const ScanPara
   }
   TO* out = static_cast<TO*>(p.out);
   const int cc = live ? c : 0;
+  float dt_sum = 0.0f;
   for (int t = first; t < last; ++t) {
     const float pre = p.dt_pre[static_cast<size_t>(t) * p.channels + cc];
     const float x = p.x[static_cast<size_t>(t) * p.channels + cc];
@@ -71,6 +114,7 @@ __global__ void __launch_bounds__(kScanThreads) mamba_scan_kernel(const ScanPara
     const float* b_row = p.bc + static_cast<size_t>(t) * 2 * p.states;
     const float* c_row = b_row + p.states;
     const float dtx = dt * x;
+    dt_sum += dt;
     float y = 0.0f;
 #pragma unroll
     for (int j = 0; j < NPL; ++j) {
@@ -80,6 +124,7 @@ __global__ void __launch_bounds__(kScanThreads) mamba_scan_kernel(const ScanPara
         y = fmaf(s[j], c_row[n], y);
       }
     }
+    if (p.mode == 1) continue;   // the pass that only finds the chunks' end states
     for (int offset = lanes >> 1; offset > 0; offset >>= 1) y += __shfl_xor_sync(0xffffffffu, y, offset);
     if (live && sub == 0) {
       const float gate = p.z[static_cast<size_t>(t) * p.z_stride + p.z_offset + c];
@@ -87,13 +132,41 @@ __global__ void __launch_bounds__(kScanThreads) mamba_scan_kernel(const ScanPara
       out[static_cast<size_t>(t) * p.channels + c] = from_float<TO>(y * (gate / (1.0f + expf(-gate))));
     }
   }
-  if (live) {
+  if (live && p.mode != 3) {
 #pragma unroll
     for (int j = 0; j < NPL; ++j) {
       const int n = sub * NPL + j;
       if (n < p.states) state[static_cast<size_t>(c) * p.states + n] = s[j];
     }
+    if (p.mode == 1 && sub == 0) p.chunk_dt[static_cast<size_t>(blockIdx.y) * p.channels + c] = dt_sum;
   }
+}
+
+// Between the two chunk passes: per entry and state element, the states at the chunks' starts one
+// after another (they take the end states' places), and the request's new state.
+__global__ void __launch_bounds__(kScanThreads) mamba_chunk_starts_kernel(const ScanParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t width = static_cast<size_t>(p.channels) * p.states;
+  const size_t item = static_cast<size_t>(blockIdx.x) * kScanThreads + threadIdx.x;
+  const int entry = blockIdx.y;
+  if (item >= width) return;
+  const int begin = p.entry_starts[entry], count = p.entry_starts[entry + 1] - begin;
+  if (count <= 0) return;
+  int job = 0;
+  for (int e = 0; e < entry; ++e) job += (p.entry_starts[e + 1] - p.entry_starts[e] + kScanChunk - 1) / kScanChunk;
+  const int chunks = (count + kScanChunk - 1) / kScanChunk;
+  const int c = static_cast<int>(item / p.states);
+  const float a = p.a[item];
+  float* state = p.state + static_cast<size_t>(p.state_slots[entry]) * width + item;
+  float s = p.fresh[entry] ? 0.0f : *state;
+  for (int k = 0; k < chunks; ++k, ++job) {
+    float* cell = p.chunk_state + static_cast<size_t>(job) * width + item;
+    const float end_state = *cell;
+    *cell = s;
+    s = fmaf(expf(a * p.chunk_dt[static_cast<size_t>(job) * p.channels + c]), s, end_state);
+  }
+  *state = s;
 }
 
 // How the states of a channel are dealt to lanes: (lanes, states per lane).
@@ -115,17 +188,31 @@ VIPERA_API int vipera_mamba_scan(const ScanParams* params, int out_dtype, void* 
   int per_lane = 1;
   scan_shape(p.states, &p.lanes, &per_lane);
   const int channels_per_block = kScanThreads / p.lanes;
-  dim3 grid((p.channels + channels_per_block - 1) / channels_per_block, p.num_entries);
+  const bool chunked = p.num_jobs > 0 && p.chunk_state && p.chunk_dt;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (out_dtype != VIPERA_BF16 && out_dtype != VIPERA_F32) return VIPERA_BAD_DTYPE;
+  auto pass = [&](int mode) -> int {
+    p.mode = mode;
+    dim3 grid((p.channels + channels_per_block - 1) / channels_per_block, mode == 0 ? p.num_entries : p.num_jobs);
 #define SCAN_CASE(N)                                                                                     \
   if (per_lane == N) {                                                                                   \
     if (out_dtype == VIPERA_BF16) return vipera_launch(mamba_scan_kernel<__nv_bfloat16, N>, grid, kScanThreads, 0, s, p); \
-    if (out_dtype == VIPERA_F32) return vipera_launch(mamba_scan_kernel<float, N>, grid, kScanThreads, 0, s, p);          \
-    return VIPERA_BAD_DTYPE;                                                                             \
+    return vipera_launch(mamba_scan_kernel<float, N>, grid, kScanThreads, 0, s, p);                       \
   }
-  SCAN_CASE(1) SCAN_CASE(2) SCAN_CASE(4) SCAN_CASE(8) SCAN_CASE(16)
+    SCAN_CASE(1) SCAN_CASE(2) SCAN_CASE(4) SCAN_CASE(8) SCAN_CASE(16)
 #undef SCAN_CASE
-  return VIPERA_BAD_SHAPE;
+    return VIPERA_BAD_SHAPE;
+  };
+  if (!chunked) return pass(0);
+  int status = pass(1);
+  if (status) return status;
+  const size_t width = static_cast<size_t>(p.channels) * p.states;
+  status = vipera_launch(mamba_chunk_starts_kernel, dim3(static_cast<unsigned>((width + kScanThreads - 1) / kScanThreads), p.num_entries),
+                         kScanThreads, 0, s, p);
+  if (status) return status;
+  return pass(3);
 }
+
+VIPERA_API int vipera_mamba_scan_chunk() { return kScanChunk; }
 
 VIPERA_API int vipera_mamba_scan_params_size() { return static_cast<int>(sizeof(ScanParams)); }

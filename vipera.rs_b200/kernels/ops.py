@@ -1146,14 +1146,30 @@ def qk_prepare(qkv: torch.Tensor, q_out: torch.Tensor, *, num_heads: int, num_kv
 TALK_MAX_HEADS = 64
 
 
+@functools.lru_cache(maxsize=4096)
+def talk_splits(tokens: int, max_keys: int, sm_count: int):
+    """How the keys of attention_talk are cut: (keys per split, splits).  A block is a (token,
+    split); steps of many tokens need no cut, steps of few tokens get enough splits for two
+    blocks an SM, of at least 64 keys each."""
+    wanted = max(1, -(-2 * sm_count // max(tokens, 1)))
+    splits = max(1, min(wanted, -(-max(max_keys, 1) // 64)))
+    keys = -(-(-(-max(max_keys, 1) // splits)) // 32) * 32
+    return keys, max(1, -(-max(max_keys, 1) // keys))
+
+
 def attention_talk(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, mix: torch.Tensor, *,
                    token_seq: torch.Tensor, positions: torch.Tensor, block_table: torch.Tensor, num_heads: int,
-                   num_kv_heads: int, head_dim: int, value_dim: int, scale: float, out_scale: float = 1.0) -> None:
+                   num_kv_heads: int, head_dim: int, value_dim: int, scale: float, out_scale: float = 1.0,
+                   split_keys: int, num_splits: int, stats: torch.Tensor, partial: Optional[torch.Tensor]) -> None:
     """Causal softmax attention whose normalised head weights are mixed by ``mix`` [heads, heads]
-    (``w_h = sum_g mix[h, g] p_g``) before head h applies them to the values of its own KV head."""
+    (``w_h = sum_g mix[h, g] p_g``) before head h applies them to the values of its own KV head.
+    The keys are cut into ``num_splits`` splits of ``split_keys`` keys (see ``talk_splits``; every
+    position of the step must lie below their product); ``stats`` is a float32 scratch of
+    2 * tokens * splits * heads values and ``partial`` one of splits * tokens * heads * value_dim
+    (needed with more than one split)."""
     fn = _function("attention_talk", "vipera_attention_talk",
                    [_c_void, _c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int,
-                    _c_int, _c_int, _c_int, _c_int, _c_float, _c_float, _c_void])
+                    _c_int, _c_int, _c_int, _c_int, _c_float, _c_float, _c_int, _c_int, _c_void, _c_void, _c_void])
     count = q.shape[0]
     if num_heads > TALK_MAX_HEADS:
         raise UnsupportedError(f"attention_talk: {num_heads} heads; the kernel takes up to {TALK_MAX_HEADS}")
@@ -1165,11 +1181,15 @@ def attention_talk(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_p
         raise InvalidArgumentError("attention_talk: cache pools do not match q and the head sizes")
     if tuple(mix.shape) != (num_heads, num_heads):
         raise InvalidArgumentError("attention_talk: the mixing matrix must be [heads, heads]")
+    if stats.numel() < 2 * count * num_splits * num_heads or \
+            (num_splits > 1 and (partial is None or partial.numel() < num_splits * count * num_heads * value_dim)):
+        raise InvalidArgumentError("attention_talk: a scratch buffer is too small")
     _check(fn(_gpu(q, "q"), _gpu(out, "out"), dtype_code(q.dtype), _gpu(k_pool, "k_pool"), _gpu(v_pool, "v_pool"),
               _gpu(mix, "mix", torch.float32), _gpu(token_seq, "token_seq", torch.int32),
               _gpu(positions, "positions", torch.int32), _gpu(block_table, "block_table", torch.int32),
               block_table.shape[1], page_size, count, num_heads, num_kv_heads, head_dim, value_dim, float(scale),
-              float(out_scale), _stream()), "attention")
+              float(out_scale), int(split_keys), int(num_splits), _gpu(stats, "stats", torch.float32),
+              _opt(partial, "partial", torch.float32), _stream()), "attention", kernels=2 if num_splits == 1 else 3)
 
 
 # ----------------------------------------------------------------------------------------
@@ -1181,17 +1201,29 @@ class _ScanParams(ctypes.Structure):
         ("z_offset", _c_int), ("a", _c_void), ("d", _c_void), ("state", _c_void), ("entry_starts", _c_void),
         ("state_slots", _c_void), ("fresh", _c_void), ("out", _c_void),
         ("channels", _c_int), ("states", _c_int), ("num_entries", _c_int), ("lanes", _c_int),
+        ("mode", _c_int), ("num_jobs", _c_int), ("chunk_state", _c_void), ("chunk_dt", _c_void),
     ]
+
+
+SCAN_CHUNK = 64   # tokens of a chunk in the recurrences' chunked forms (kScanChunk in mamba.cu, kGlaChunk in gla.cu)
+
+
+def scan_jobs(tokens: int, num_entries: int) -> int:
+    """The most chunks a step of `tokens` tokens in `num_entries` entries has."""
+    return tokens // SCAN_CHUNK + num_entries
 
 
 def mamba_scan(x: torch.Tensor, dt_pre: torch.Tensor, bc: torch.Tensor, z: torch.Tensor, z_offset: int, *,
                a: torch.Tensor, d: torch.Tensor, state: torch.Tensor, entry_starts: torch.Tensor,
-               state_slots: torch.Tensor, fresh: torch.Tensor, num_entries: int, out: torch.Tensor) -> None:
+               state_slots: torch.Tensor, fresh: torch.Tensor, num_entries: int, out: torch.Tensor,
+               chunk_scratch=None) -> None:
     """Mamba's selective scan.  ``x`` (after convolution and silu) and ``dt_pre`` (the step-size
     product with its bias, before softplus) are float32 [tokens, channels]; ``bc`` float32 [tokens,
     2 * states] holds B then C; the gate's pre-activation is column ``z_offset + c`` of the float32
     ``z``; ``a`` [channels, states] is -exp(A_log), ``d`` [channels]; ``state`` float32 [slots,
-    channels * states]; ``out`` [tokens, channels] receives y * silu(z)."""
+    channels * states]; ``out`` [tokens, channels] receives y * silu(z).  ``chunk_scratch`` (float32
+    tensors [jobs, channels * states] and [jobs, channels] with jobs >= scan_jobs(tokens, entries))
+    lets the step's chunks of SCAN_CHUNK tokens run side by side instead of each entry's tokens in a row."""
     fn = _function("mamba", "vipera_mamba_scan", [ctypes.POINTER(_ScanParams), _c_int, _c_void])
     _check_struct("mamba", "vipera_mamba_scan_params_size", _ScanParams)
     tokens, channels = x.shape
@@ -1213,7 +1245,15 @@ def mamba_scan(x: torch.Tensor, dt_pre: torch.Tensor, bc: torch.Tensor, z: torch
     p.fresh = _gpu(fresh, "fresh", torch.int32)
     p.out = _gpu(out, "out")
     p.channels, p.states, p.num_entries = int(channels), int(states), int(num_entries)
-    _check(fn(ctypes.byref(p), dtype_code(out.dtype), _stream()), "mamba_scan")
+    if chunk_scratch is not None:
+        chunk_state, chunk_dt = chunk_scratch
+        jobs = scan_jobs(tokens, num_entries)
+        if chunk_state.shape[0] < jobs or chunk_dt.shape[0] < jobs or chunk_state.shape[1] != channels * states or \
+                chunk_dt.shape[1] != channels:
+            raise InvalidArgumentError("mamba_scan: the chunk scratch has the wrong shape")
+        p.num_jobs = jobs
+        p.chunk_state, p.chunk_dt = _gpu(chunk_state, "chunk states", torch.float32), _gpu(chunk_dt, "chunk dt", torch.float32)
+    _check(fn(ctypes.byref(p), dtype_code(out.dtype), _stream()), "mamba_scan", kernels=3 if chunk_scratch is not None else 1)
 
 
 class _GlaParams(ctypes.Structure):
@@ -1224,6 +1264,7 @@ class _GlaParams(ctypes.Structure):
         ("partial", _c_void), ("norm_weight", _c_void), ("out", _c_void),
         ("heads", _c_int), ("dim", _c_int), ("vdim", _c_int), ("num_entries", _c_int), ("num_tokens", _c_int),
         ("shares", _c_int), ("q_scale", _c_float), ("inv_tau", _c_float), ("eps", _c_float), ("out_scale", _c_float),
+        ("mode", _c_int), ("num_jobs", _c_int), ("chunk_state", _c_void), ("chunk_decay", _c_void),
     ]
 
 
@@ -1236,12 +1277,15 @@ def gla_shares(dim: int) -> int:
 
 def gla(proj: torch.Tensor, z: torch.Tensor, *, offsets, heads: int, dim: int, vdim: int, q_scale: float, tau: float,
         norm_weight: torch.Tensor, norm_eps: float, out_scale: float, state: torch.Tensor, entry_starts: torch.Tensor,
-        state_slots: torch.Tensor, fresh: torch.Tensor, num_entries: int, partial: torch.Tensor, out: torch.Tensor) -> None:
+        state_slots: torch.Tensor, fresh: torch.Tensor, num_entries: int, partial: torch.Tensor, out: torch.Tensor,
+        chunk_scratch=None) -> None:
     """Gated linear attention over a step.  ``proj`` float32 [tokens, width] holds q, k, v and the
     output gate's pre-activation at ``offsets``; ``z`` float32 [tokens, heads * dim] the decays'
     pre-activations; ``state`` float32 [slots, heads * dim * vdim]; ``partial`` float32 scratch of
     gla_shares(dim) * tokens * heads * vdim values; ``out`` [tokens, heads * vdim] receives the
-    normalised, gated and scaled output."""
+    normalised, gated and scaled output.  ``chunk_scratch`` (float32 tensors [jobs, heads * dim * vdim]
+    and [jobs, heads * dim] with jobs >= scan_jobs(tokens, entries)) lets the step's chunks of SCAN_CHUNK
+    tokens run side by side instead of each entry's tokens in a row."""
     fn = _function("gla", "vipera_gla", [ctypes.POINTER(_GlaParams), _c_int, _c_void])
     _check_struct("gla", "vipera_gla_params_size", _GlaParams)
     tokens = proj.shape[0]
@@ -1263,4 +1307,13 @@ def gla(proj: torch.Tensor, z: torch.Tensor, *, offsets, heads: int, dim: int, v
     p.out = _gpu(out, "out")
     p.heads, p.dim, p.vdim, p.num_entries, p.num_tokens = int(heads), int(dim), int(vdim), int(num_entries), int(tokens)
     p.q_scale, p.inv_tau, p.eps, p.out_scale = float(q_scale), 1.0 / float(tau), float(norm_eps), float(out_scale)
-    _check(fn(ctypes.byref(p), dtype_code(out.dtype), _stream()), "gla", kernels=2)
+    if chunk_scratch is not None:
+        chunk_state, chunk_decay = chunk_scratch
+        jobs = scan_jobs(tokens, num_entries)
+        if chunk_state.shape[0] < jobs or chunk_decay.shape[0] < jobs or chunk_state.shape[1] != heads * dim * vdim or \
+                chunk_decay.shape[1] != heads * dim:
+            raise InvalidArgumentError("gla: the chunk scratch has the wrong shape")
+        p.num_jobs = jobs
+        p.chunk_state = _gpu(chunk_state, "chunk states", torch.float32)
+        p.chunk_decay = _gpu(chunk_decay, "chunk decays", torch.float32)
+    _check(fn(ctypes.byref(p), dtype_code(out.dtype), _stream()), "gla", kernels=4 if chunk_scratch is not None else 2)

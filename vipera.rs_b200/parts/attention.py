@@ -235,9 +235,15 @@ class GQAttention(Mixer):
         heads, kv_heads, d = self.num_heads, self.num_kv_heads, self.head_dim
         window = self.window or 0
         if self.talk is not None:
+            count = ctx.num_tokens
+            keys, splits = ops.talk_splits(count, max(ctx.max_kv_len, 1), ops.sm_count(q.device))
+            stats = ctx.workspace.get("attention.talk_stats", (count, splits, heads, 2), torch.float32)
+            partial = None if splits == 1 else ctx.workspace.get(
+                "attention.talk_partial", (splits, count, heads * self.value_dim), torch.float32)
             ops.attention_talk(q, mixed, cache.k, cache.v, self.talk, token_seq=ctx.token_entry,
                                positions=ctx.positions, block_table=table, num_heads=heads, num_kv_heads=kv_heads,
-                               head_dim=d, value_dim=self.value_dim, scale=self.scale, out_scale=self.out_scale)
+                               head_dim=d, value_dim=self.value_dim, scale=self.scale, out_scale=self.out_scale,
+                               split_keys=keys, num_splits=splits, stats=stats, partial=partial)
             return
         if self.out_scale == 1.0 and ctx.dtype == torch.bfloat16 and d in ops.MMA_HEAD_DIMS and self.value_dim == d:
             # Kept first keys and the sink are options of the mma.sync kernels (the flash kernel folds

@@ -15,6 +15,8 @@ come from one product with the concatenated matrix; its result stays 32-bit, and
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..config.registry import MIXERS
@@ -31,6 +33,9 @@ class GatedLinearAttention(Mixer):
     q, k, v, g, o, norm [value_dim], a1 [rank, hidden], a2 [heads * head_dim, rank] with a bias."""
 
     kernels = ("gla",)
+    # Steps of this many tokens and more run their chunks side by side (the recurrence computed
+    # twice); shorter ones walk each entry's tokens in one launch.
+    CHUNKED_FROM = int(os.environ.get("VIPERA_SCAN_CHUNKED_FROM", 256))
 
     @classmethod
     def schema(cls, params, prefix):
@@ -94,10 +99,16 @@ class GatedLinearAttention(Mixer):
         self.decay_out(ctx, low, epilogue=ops.EPI_STORE, out=z)
         partial = ws.get("gla.partial", (ops.gla_shares(self.dim), count, self.heads * self.vdim), torch.float32)
         mixed = ws.get("gla.out", (count, self.heads * self.vdim), ctx.dtype)
+        chunk_scratch = None
+        if not ctx.all_single and count >= self.CHUNKED_FROM:
+            jobs = ops.scan_jobs(count, ctx.num_entries)
+            chunk_scratch = (ws.get("gla.chunk_states", (jobs, self.heads * self.dim * self.vdim), torch.float32),
+                             ws.get("gla.chunk_decays", (jobs, self.heads * self.dim), torch.float32))
         ops.gla(proj, z, offsets=self.offsets, heads=self.heads, dim=self.dim, vdim=self.vdim,
                 q_scale=self.dim ** -0.5, tau=self.tau, norm_weight=self.norm_weight, norm_eps=self.norm_eps,
                 out_scale=self.out_scale, state=cache.data, entry_starts=ctx.entry_starts,
-                state_slots=ctx.state_slots, fresh=ctx.fresh, num_entries=ctx.num_entries, partial=partial, out=mixed)
+                state_slots=ctx.state_slots, fresh=ctx.fresh, num_entries=ctx.num_entries, partial=partial, out=mixed,
+                chunk_scratch=chunk_scratch)
         self.out(ctx, mixed, epilogue=ops.EPI_RESIDUAL, resid=residual)
 
 

@@ -13,6 +13,8 @@ arithmetic is 32-bit throughout: softplus, exp(dt A), the state and the sums ove
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..config.registry import MIXERS
@@ -29,6 +31,9 @@ class Mamba1(Mixer):
     ``<prefix>``: in, conv (+ bias), x, dt (+ bias), A_log, D, o."""
 
     kernels = ("mamba", "seqconv")
+    # Steps of this many tokens and more run their chunks side by side (three launches, the
+    # recurrence computed twice); shorter ones walk each entry's tokens in one launch.
+    CHUNKED_FROM = int(os.environ.get("VIPERA_SCAN_CHUNKED_FROM", 256))
 
     @classmethod
     def schema(cls, params, prefix):
@@ -98,9 +103,14 @@ class Mamba1(Mixer):
         dt_pre = ws.get("mamba.dt", (count, self.inner), torch.float32)
         self.proj_dt(ctx, dt_low, epilogue=ops.EPI_STORE, out=dt_pre)
         y = ws.get("mamba.y", (count, self.inner), ctx.dtype)
+        chunk_scratch = None
+        if not ctx.all_single and count >= self.CHUNKED_FROM:
+            jobs = ops.scan_jobs(count, ctx.num_entries)
+            chunk_scratch = (ws.get("mamba.chunk_states", (jobs, self.inner * self.state), torch.float32),
+                             ws.get("mamba.chunk_dt", (jobs, self.inner), torch.float32))
         ops.mamba_scan(x32, dt_pre, bc, xz, self.inner, a=self.a, d=self.d, state=cache["scan"].data,
                        entry_starts=ctx.entry_starts, state_slots=ctx.state_slots, fresh=ctx.fresh,
-                       num_entries=ctx.num_entries, out=y)
+                       num_entries=ctx.num_entries, out=y, chunk_scratch=chunk_scratch)
         self.out(ctx, y, epilogue=ops.EPI_RESIDUAL, resid=residual)
 
 
