@@ -34,14 +34,18 @@ __device__ __forceinline__ int first_visible_key(int position, int window) {
 // ---------------------------------------------------------------------------------------
 // HPC: query heads per block (1 or 2).  Two heads of the same KV group share every key and
 // value tile the block loads; the block then has eight warps, four per head.
-template <int D, int HPC>
+// VIRT: "virtual heads".  Block row u stands for query head u / v_heads read against the values of
+// KV head u % v_heads (the keys stay those of the query head's own KV head), and writes row u of an
+// output of num_heads * v_heads heads: softmax(q_g k^T) v_c for every pair (g, c), which a mix of
+// the heads' weights behind the softmax is a linear combination of.
+template <int D, int HPC, bool VIRT = false>
 __global__ void __launch_bounds__(128 * HPC)
 attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
                          const __nv_bfloat16* __restrict__ k_pool, const __nv_bfloat16* __restrict__ v_pool,
                          const int* __restrict__ entry_starts, const int* __restrict__ entry_pos0,
                          const int* __restrict__ block_table, int table_width, int page_size, int num_entries,
                          int num_heads, int num_kv_heads, float scale, int window, int skip_single,
-                         int keep_first, int sink) {
+                         int keep_first, int sink, int v_heads) {
   // keep_first: with a window, keys 0 .. keep_first-1 stay visible to every later query.  The
   // block folds them first, as tiles of their own with a mask of their own (keys below both
   // keep_first and the row's window), then the window's tiles as ever.  sink != 0: a key of
@@ -65,9 +69,12 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
   }
   if (entry < 0) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int head = blockIdx.y * HPC + (warp >> 2);  // this warp's query head
+  const int head = VIRT ? blockIdx.y : blockIdx.y * HPC + (warp >> 2);  // this warp's head in the output
+  const int q_head0 = VIRT ? blockIdx.y / v_heads : blockIdx.y * HPC;    // the block's first query head
+  const int out_heads = VIRT ? num_heads * v_heads : num_heads;
   const int q_warp = warp & 3;                       // which 16 of the 64 queries
-  const int kv_head = (blockIdx.y * HPC) / (num_heads / num_kv_heads);
+  const int kv_head = q_head0 / (num_heads / num_kv_heads);
+  const int v_head = VIRT ? blockIdx.y % v_heads : kv_head;
   const int token0 = entry_starts[entry] + tile_in_entry * kQ;
   const int tokens_here = min(kQ, entry_starts[entry + 1] - token0);
   const int pos0 = entry_pos0[entry] + tile_in_entry * kQ;  // position of the tile's first query
@@ -84,7 +91,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
       const int which = index / (kQ * kChunks);
       const int row = (index / kChunks) % kQ, chunk = index % kChunks;
       const bool valid = row < tokens_here;
-      const __nv_bfloat16* src = q + (static_cast<size_t>(token0 + (valid ? row : 0)) * num_heads + blockIdx.y * HPC + which) * D + chunk * 8;
+      const __nv_bfloat16* src = q + (static_cast<size_t>(token0 + (valid ? row : 0)) * num_heads + q_head0 + which) * D + chunk * 8;
       cp_async_16(q_tiles + which * kQ * D * 2 + tile_offset<D>(row, chunk), src, valid);
     }
   }
@@ -103,7 +110,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
     const int from = kept ? 0 : first_key, to = kept ? kept_end : end_key;
     load_kv_tile<D, kKeys, kThreads>(k_tiles + buffer * kKeys * D * 2, k_pool, table, page_size, num_kv_heads, kv_head,
                                      key0, from, to, threadIdx.x);
-    load_kv_tile<D, kKeys, kThreads>(v_tiles + buffer * kKeys * D * 2, v_pool, table, page_size, num_kv_heads, kv_head,
+    load_kv_tile<D, kKeys, kThreads>(v_tiles + buffer * kKeys * D * 2, v_pool, table, page_size, num_kv_heads, v_head,
                                      key0, from, to, threadIdx.x);
   };
   load_block(0, 0);
@@ -162,7 +169,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
     if (row >= tokens_here) continue;
     if (sink) sum += exp2f(-row_max[r]);   // the sink's score is 0; the maximum is in units of log2
     const float inverse = 1.0f / sum;
-    __nv_bfloat16* dst = out + (static_cast<size_t>(token0 + row) * num_heads + head) * D;
+    __nv_bfloat16* dst = out + (static_cast<size_t>(token0 + row) * out_heads + head) * D;
 #pragma unroll
     for (int n = 0; n < D / 8; ++n) {
       const int col = n * 8 + 2 * (lane & 3);
@@ -651,7 +658,26 @@ int launch_prefill_variant(const void* q, void* out, const void* k_pool, const v
   return vipera_launch(attention_prefill_kernel<D, HPC>, grid, dim3(128 * HPC), kSmem, s,
       static_cast<const __nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(k_pool),
       static_cast<const __nv_bfloat16*>(v_pool), entry_starts, entry_pos0, block_table, table_width, page_size,
-      num_entries, num_heads, num_kv_heads, scale, window, skip_single, keep_first, sink);
+      num_entries, num_heads, num_kv_heads, scale, window, skip_single, keep_first, sink, 0);
+}
+
+// Every pair (query head, KV head for the values) as a head of its own: out is [tokens, heads * kv_heads, D].
+template <int D>
+int launch_prefill_virtual(const void* q, void* out, const void* k_pool, const void* v_pool, const int* entry_starts,
+                           const int* entry_pos0, const int* block_table, int table_width, int page_size,
+                           int num_entries, int num_tokens, int num_heads, int num_kv_heads, float scale, cudaStream_t s) {
+  constexpr int kSmem = (64 + 4 * 64) * D * 2;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<D, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  dim3 grid((num_tokens + 63) / 64 + num_entries, num_heads * num_kv_heads);
+  return vipera_launch(attention_prefill_kernel<D, 1, true>, grid, dim3(128), kSmem, s,
+      static_cast<const __nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(k_pool),
+      static_cast<const __nv_bfloat16*>(v_pool), entry_starts, entry_pos0, block_table, table_width, page_size,
+      num_entries, num_heads, num_kv_heads, scale, 0, 0, 0, 0, num_kv_heads);
 }
 
 template <int D>
@@ -811,6 +837,25 @@ static int run_prefill(const void* q, void* out, const void* k_pool, const void*
     return launch_prefill<64>(q, out, k_pool, v_pool, entry_starts, entry_pos0, block_table, table_width, page_size,
                               num_entries, num_tokens, num_heads, num_kv_heads, scale, window, skip_single, keep_first,
                               sink, s);
+  return VIPERA_BAD_SHAPE;
+}
+
+// Causal attention of every query head against the values of every KV head (keys: the query head's
+// own KV head): out [tokens, heads * kv_heads, d], row g * kv_heads + c = softmax(q_g k^T) v_c.
+VIPERA_API int vipera_attention_prefill_pairs(const void* q, void* out, const void* k_pool, const void* v_pool,
+                                              const int* entry_starts, const int* entry_pos0, const int* block_table,
+                                              int table_width, int page_size, int num_entries, int num_tokens,
+                                              int num_heads, int num_kv_heads, int head_dim, float scale, void* stream) {
+  if (num_tokens <= 0 || num_entries <= 0) return VIPERA_OK;
+  if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads) return VIPERA_BAD_SHAPE;
+  if (static_cast<long>(num_heads) * num_kv_heads > 65535) return VIPERA_BAD_SHAPE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (head_dim == 128)
+    return launch_prefill_virtual<128>(q, out, k_pool, v_pool, entry_starts, entry_pos0, block_table, table_width,
+                                       page_size, num_entries, num_tokens, num_heads, num_kv_heads, scale, s);
+  if (head_dim == 64)
+    return launch_prefill_virtual<64>(q, out, k_pool, v_pool, entry_starts, entry_pos0, block_table, table_width,
+                                      page_size, num_entries, num_tokens, num_heads, num_kv_heads, scale, s);
   return VIPERA_BAD_SHAPE;
 }
 

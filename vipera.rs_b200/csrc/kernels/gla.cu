@@ -25,13 +25,16 @@
 // re-associates 32-bit sums.  Chunks are counted from where an entry's tokens start in the step.
 #include "common.cuh"
 
+#include <algorithm>
+
 constexpr int kGlaMaxShares = 16;
 
 struct GlaParams {
   const float* proj;      // [tokens, proj_width]: q, k, v, g at their offsets
   long long proj_width;
   int q_off, k_off, v_off, g_off;
-  const float* z;         // [tokens, heads * dim]  decay pre-activations (bias included)
+  float* z;               // [tokens, heads * dim]  decay pre-activations (bias included); the decays take their place
+  float* log_alpha;       // [tokens, heads * dim]  receives the decays' logarithms
   float* state;           // [slots, heads * dim * vdim]
   const int* entry_starts;
   const int* state_slots;
@@ -64,6 +67,20 @@ __device__ __forceinline__ bool gla_job(const int* __restrict__ entry_starts, in
     before += chunks;
   }
   return false;
+}
+
+// alpha = sigmoid(z)^(1 / tau) through log sigmoid(z) = min(z, 0) - log1p(exp(-|z|)), once per token
+// and key channel: alpha takes z's place, its logarithm goes beside it.
+__global__ void __launch_bounds__(256) gla_decay_kernel(const GlaParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t count = static_cast<size_t>(p.num_tokens) * p.heads * p.dim;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * 256 + threadIdx.x; i < count; i += static_cast<size_t>(gridDim.x) * 256) {
+    const float zz = p.z[i];
+    const float log_alpha = (fminf(zz, 0.0f) - log1pf(expf(-fabsf(zz)))) * p.inv_tau;
+    p.log_alpha[i] = log_alpha;
+    p.z[i] = expf(log_alpha);
+  }
 }
 
 template <int ROWS>
@@ -104,17 +121,15 @@ __global__ void __launch_bounds__(kGlaMaxShares * 32) gla_scan_kernel(const GlaP
     const float* row = p.proj + static_cast<size_t>(t) * p.proj_width;
     const float* q = row + p.q_off + head * p.dim + row0;
     const float* k = row + p.k_off + head * p.dim + row0;
-    const float* z = p.z + (static_cast<size_t>(t) * p.heads + head) * p.dim + row0;
+    const size_t decay_at = (static_cast<size_t>(t) * p.heads + head) * p.dim + row0;
+    const float* alpha = p.z + decay_at;
     const float v = live ? row[p.v_off + head * p.vdim + column] : 0.0f;
     float o = 0.0f;
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) {
       if (row0 + r < p.dim) {
-        // log sigmoid(z) = min(z, 0) - log1p(exp(-|z|))
-        const float zz = z[r];
-        const float log_alpha = (fminf(zz, 0.0f) - log1pf(expf(-fabsf(zz)))) * p.inv_tau;
-        log_decay[r] += log_alpha;
-        s[r] = fmaf(expf(log_alpha), s[r], k[r] * v);
+        if (p.mode == 1) log_decay[r] += p.log_alpha[decay_at + r];
+        s[r] = fmaf(alpha[r], s[r], k[r] * v);
         o = fmaf(s[r], q[r] * p.q_scale, o);
       }
     }
@@ -194,7 +209,7 @@ VIPERA_API int vipera_gla(const GlaParams* params, int out_dtype, void* stream) 
   GlaParams p = *params;
   if (p.num_tokens <= 0 || p.num_entries <= 0) return VIPERA_OK;
   if (p.heads <= 0 || p.dim <= 0 || p.dim > 512 || p.vdim <= 0) return VIPERA_BAD_SHAPE;
-  if (!p.proj || !p.z || !p.state || !p.entry_starts || !p.state_slots || !p.fresh || !p.partial || !p.norm_weight || !p.out)
+  if (!p.proj || !p.z || !p.log_alpha || !p.state || !p.entry_starts || !p.state_slots || !p.fresh || !p.partial || !p.norm_weight || !p.out)
     return VIPERA_BAD_ARGUMENT;
   const int rows = gla_rows(p.dim);
   p.shares = (p.dim + rows - 1) / rows;
@@ -208,7 +223,9 @@ VIPERA_API int vipera_gla(const GlaParams* params, int out_dtype, void* stream) 
     if (rows == 16) return vipera_launch(gla_scan_kernel<16>, grid, p.shares * 32, 0, s, p);
     return vipera_launch(gla_scan_kernel<32>, grid, p.shares * 32, 0, s, p);
   };
-  int status;
+  const size_t decays = static_cast<size_t>(p.num_tokens) * p.heads * p.dim;
+  int status = vipera_launch(gla_decay_kernel, dim3(static_cast<unsigned>(std::min<size_t>((decays + 255) / 256, 4096))), 256, 0, s, p);
+  if (status) return status;
   if (!chunked) status = pass(0);
   else {
     status = pass(1);

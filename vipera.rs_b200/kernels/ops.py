@@ -1192,6 +1192,37 @@ def attention_talk(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_p
               _opt(partial, "partial", torch.float32), _stream()), "attention", kernels=2 if num_splits == 1 else 3)
 
 
+def attention_talk_prefill(q: torch.Tensor, out: torch.Tensor, pairs: torch.Tensor, k_pool: torch.Tensor,
+                           v_pool: torch.Tensor, mix: torch.Tensor, *, entry_starts: torch.Tensor, entry_pos0: torch.Tensor,
+                           block_table: torch.Tensor, num_entries: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                           scale: float, out_scale: float = 1.0) -> None:
+    """The same result as ``attention_talk`` for steps with portions, on the tensor cores (bfloat16,
+    head sizes 64 and 128, values as long as keys): the flash kernel computes softmax(q_g k^T) v_c
+    for every pair of a query head g and a KV head c into ``pairs`` [tokens, heads * kv_heads * d],
+    and a second kernel forms ``out[t, h] = out_scale * sum_g mix[h, g] pairs[t, g, kv(h)]`` in 32-bit
+    (mixing the heads' weights is linear in them, and the values are shared)."""
+    if head_dim not in MMA_HEAD_DIMS:
+        raise UnsupportedError(f"attention_talk_prefill: head size {head_dim} (built: 64, 128)")
+    count = q.shape[0]
+    if q.shape[1] != num_heads * head_dim or out.shape != q.shape or \
+            tuple(pairs.shape) != (count, num_heads * num_kv_heads * head_dim):
+        raise InvalidArgumentError("attention_talk_prefill: q and out must be [tokens, heads * d], pairs [tokens, heads * kv_heads * d]")
+    if k_pool.shape[2:] != (num_kv_heads, head_dim) or v_pool.shape != k_pool.shape:
+        raise InvalidArgumentError("attention_talk_prefill: cache pools must be [pages, page_size, kv_heads, d]")
+    if tuple(mix.shape) != (num_heads, num_heads):
+        raise InvalidArgumentError("attention_talk_prefill: the mixing matrix must be [heads, heads]")
+    fn = _function("attention_mma", "vipera_attention_prefill_pairs", [_c_void] * 7 + [_c_int] * 7 + [_c_float, _c_void])
+    _check(fn(_gpu(q, "q", torch.bfloat16), _gpu(pairs, "pairs", torch.bfloat16), _gpu(k_pool, "k_pool", torch.bfloat16),
+              _gpu(v_pool, "v_pool", torch.bfloat16), _gpu(entry_starts, "entry_starts", torch.int32),
+              _gpu(entry_pos0, "entry_pos0", torch.int32), _gpu(block_table, "block_table", torch.int32),
+              block_table.shape[1], k_pool.shape[1], int(num_entries), count, num_heads, num_kv_heads, head_dim,
+              float(scale), _stream()), "attention_prefill")
+    fn = _function("attention_talk", "vipera_talk_combine",
+                   [_c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void])
+    _check(fn(pairs.data_ptr(), _gpu(mix, "mix", torch.float32), _gpu(out, "out", torch.bfloat16), BF16, count, num_heads,
+              num_kv_heads, head_dim, float(out_scale), _stream()), "attention")
+
+
 # ----------------------------------------------------------------------------------------
 # recurrences with a state of fixed size: Mamba's selective scan, gated linear attention
 # ----------------------------------------------------------------------------------------
@@ -1260,8 +1291,8 @@ class _GlaParams(ctypes.Structure):
     _fields_ = [
         ("proj", _c_void), ("proj_width", ctypes.c_longlong),
         ("q_off", _c_int), ("k_off", _c_int), ("v_off", _c_int), ("g_off", _c_int),
-        ("z", _c_void), ("state", _c_void), ("entry_starts", _c_void), ("state_slots", _c_void), ("fresh", _c_void),
-        ("partial", _c_void), ("norm_weight", _c_void), ("out", _c_void),
+        ("z", _c_void), ("log_alpha", _c_void), ("state", _c_void), ("entry_starts", _c_void), ("state_slots", _c_void),
+        ("fresh", _c_void), ("partial", _c_void), ("norm_weight", _c_void), ("out", _c_void),
         ("heads", _c_int), ("dim", _c_int), ("vdim", _c_int), ("num_entries", _c_int), ("num_tokens", _c_int),
         ("shares", _c_int), ("q_scale", _c_float), ("inv_tau", _c_float), ("eps", _c_float), ("out_scale", _c_float),
         ("mode", _c_int), ("num_jobs", _c_int), ("chunk_state", _c_void), ("chunk_decay", _c_void),
@@ -1278,10 +1309,10 @@ def gla_shares(dim: int) -> int:
 def gla(proj: torch.Tensor, z: torch.Tensor, *, offsets, heads: int, dim: int, vdim: int, q_scale: float, tau: float,
         norm_weight: torch.Tensor, norm_eps: float, out_scale: float, state: torch.Tensor, entry_starts: torch.Tensor,
         state_slots: torch.Tensor, fresh: torch.Tensor, num_entries: int, partial: torch.Tensor, out: torch.Tensor,
-        chunk_scratch=None) -> None:
+        log_decay: torch.Tensor, chunk_scratch=None) -> None:
     """Gated linear attention over a step.  ``proj`` float32 [tokens, width] holds q, k, v and the
     output gate's pre-activation at ``offsets``; ``z`` float32 [tokens, heads * dim] the decays'
-    pre-activations; ``state`` float32 [slots, heads * dim * vdim]; ``partial`` float32 scratch of
+    pre-activations (the decays take their place; ``log_decay``, of the same shape, receives their logarithms); ``state`` float32 [slots, heads * dim * vdim]; ``partial`` float32 scratch of
     gla_shares(dim) * tokens * heads * vdim values; ``out`` [tokens, heads * vdim] receives the
     normalised, gated and scaled output.  ``chunk_scratch`` (float32 tensors [jobs, heads * dim * vdim]
     and [jobs, heads * dim] with jobs >= scan_jobs(tokens, entries)) lets the step's chunks of SCAN_CHUNK
@@ -1289,7 +1320,8 @@ def gla(proj: torch.Tensor, z: torch.Tensor, *, offsets, heads: int, dim: int, v
     fn = _function("gla", "vipera_gla", [ctypes.POINTER(_GlaParams), _c_int, _c_void])
     _check_struct("gla", "vipera_gla_params_size", _GlaParams)
     tokens = proj.shape[0]
-    if tuple(z.shape) != (tokens, heads * dim) or tuple(out.shape) != (tokens, heads * vdim):
+    if tuple(z.shape) != (tokens, heads * dim) or tuple(log_decay.shape) != tuple(z.shape) or \
+            tuple(out.shape) != (tokens, heads * vdim):
         raise InvalidArgumentError("gla: z must be [tokens, heads * d] and out [tokens, heads * value size]")
     if state.dim() != 2 or state.shape[1] != heads * dim * vdim:
         raise InvalidArgumentError("gla: state rows must hold heads * d * value size floats")
@@ -1299,6 +1331,7 @@ def gla(proj: torch.Tensor, z: torch.Tensor, *, offsets, heads: int, dim: int, v
     p.proj, p.proj_width = _gpu(proj, "proj", torch.float32), proj.shape[1]
     p.q_off, p.k_off, p.v_off, p.g_off = (int(o) for o in offsets)
     p.z, p.state = _gpu(z, "z", torch.float32), _gpu(state, "state", torch.float32)
+    p.log_alpha = _gpu(log_decay, "log_decay", torch.float32)
     p.entry_starts = _gpu(entry_starts, "entry_starts", torch.int32)
     p.state_slots = _gpu(state_slots, "state_slots", torch.int32)
     p.fresh = _gpu(fresh, "fresh", torch.int32)
@@ -1316,4 +1349,4 @@ def gla(proj: torch.Tensor, z: torch.Tensor, *, offsets, heads: int, dim: int, v
         p.num_jobs = jobs
         p.chunk_state = _gpu(chunk_state, "chunk states", torch.float32)
         p.chunk_decay = _gpu(chunk_decay, "chunk decays", torch.float32)
-    _check(fn(ctypes.byref(p), dtype_code(out.dtype), _stream()), "gla", kernels=4 if chunk_scratch is not None else 2)
+    _check(fn(ctypes.byref(p), dtype_code(out.dtype), _stream()), "gla", kernels=5 if chunk_scratch is not None else 3)

@@ -12,6 +12,8 @@ output product adds into the 32-bit residual stream in its own ending.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..config.registry import MIXERS, POSITION_ENCODINGS
@@ -41,6 +43,10 @@ class GQAttention(Mixer):
 
     kernels = ("rope_cache", "attention", "attention_mma", "attention_tc")
     takes_lazy_input = True
+    # With mixed head weights: steps of this many tokens and more that bring portions run every
+    # (query head, KV head) pair through the tensor-core flash kernel; shorter ones and steps of
+    # single tokens run the split-key kernels.
+    TALK_PAIRS_FROM = int(os.environ.get("VIPERA_TALK_PAIRS_FROM", 64))
 
     @staticmethod
     def _names(params):
@@ -130,6 +136,8 @@ class GQAttention(Mixer):
         own = ["rope_cache", "attention"]
         if self.talk is not None:
             own.append("attention_talk")
+            if self.dtype == torch.bfloat16 and self.head_dim in ops.MMA_HEAD_DIMS and self.value_dim == self.head_dim:
+                own.append("attention_mma")
         plain_mask = self.talk is None and self.out_scale == 1.0
         if plain_mask and self.dtype == torch.bfloat16 and self.head_dim in (64, 128) and self.value_dim == self.head_dim:
             own.append("attention_mma")
@@ -236,6 +244,16 @@ class GQAttention(Mixer):
         window = self.window or 0
         if self.talk is not None:
             count = ctx.num_tokens
+            if (not ctx.all_single and ctx.dtype == torch.bfloat16 and d in ops.MMA_HEAD_DIMS and self.value_dim == d
+                    and count >= self.TALK_PAIRS_FROM and heads * kv_heads <= 4096):
+                # steps with portions on the tensor cores: every (query head, KV head) pair through the
+                # flash kernel, then the mix of the pairs' outputs
+                pairs = ctx.workspace.get("attention.talk_pairs", (count, heads * kv_heads * d), ctx.dtype)
+                ops.attention_talk_prefill(q, mixed, pairs, cache.k, cache.v, self.talk, entry_starts=ctx.entry_starts,
+                                           entry_pos0=ctx.entry_pos0, block_table=table, num_entries=ctx.num_entries,
+                                           num_heads=heads, num_kv_heads=kv_heads, head_dim=d, scale=self.scale,
+                                           out_scale=self.out_scale)
+                return
             keys, splits = ops.talk_splits(count, max(ctx.max_kv_len, 1), ops.sm_count(q.device))
             stats = ctx.workspace.get("attention.talk_stats", (count, splits, heads, 2), torch.float32)
             partial = None if splits == 1 else ctx.workspace.get(

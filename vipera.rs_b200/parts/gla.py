@@ -97,6 +97,7 @@ class GatedLinearAttention(Mixer):
         self.decay_in(ctx, h, epilogue=ops.EPI_STORE, out=low)
         z = ws.get("gla.decay", (count, self.heads * self.dim), torch.float32)
         self.decay_out(ctx, low, epilogue=ops.EPI_STORE, out=z)
+        log_decay = ws.get("gla.log_decay", (count, self.heads * self.dim), torch.float32)
         partial = ws.get("gla.partial", (ops.gla_shares(self.dim), count, self.heads * self.vdim), torch.float32)
         mixed = ws.get("gla.out", (count, self.heads * self.vdim), ctx.dtype)
         chunk_scratch = None
@@ -108,7 +109,7 @@ class GatedLinearAttention(Mixer):
                 q_scale=self.dim ** -0.5, tau=self.tau, norm_weight=self.norm_weight, norm_eps=self.norm_eps,
                 out_scale=self.out_scale, state=cache.data, entry_starts=ctx.entry_starts,
                 state_slots=ctx.state_slots, fresh=ctx.fresh, num_entries=ctx.num_entries, partial=partial, out=mixed,
-                chunk_scratch=chunk_scratch)
+                log_decay=log_decay, chunk_scratch=chunk_scratch)
         self.out(ctx, mixed, epilogue=ops.EPI_RESIDUAL, resid=residual)
 
 
