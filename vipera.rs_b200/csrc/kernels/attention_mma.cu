@@ -183,14 +183,17 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
 // decode: block = (entry, KV head, split); rows of the tile = query heads of the group
 // ---------------------------------------------------------------------------------------
 // partial layout: [token][head][split]: max (log2 units), sum, and D unnormalised outputs.
-template <int D, bool KEPT = false>   // KEPT: the instance that knows kept first keys (the other is the kernel as it was)
+// VIRT: block column u stands for KV head u / v_heads for the keys (its group's query heads are the
+// rows) and KV head u % v_heads for the values; query head g's row lands at head g * v_heads + u %
+// v_heads of partials that have num_heads * v_heads heads (see the prefill kernel's VIRT).
+template <int D, bool KEPT = false, bool VIRT = false>   // KEPT: the instance that knows kept first keys (the other is the kernel as it was)
 __global__ void __launch_bounds__(128, 3)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
                         const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ positions,
                         const int* __restrict__ block_table, int table_width, int page_size, int page_shift,
                         int num_heads, int num_kv_heads, float scale, int window, int chunk, int num_splits,
                         float* __restrict__ partial_ml, float* __restrict__ partial_out,
-                        const int* __restrict__ entry_starts, int keep_first) {
+                        const int* __restrict__ entry_starts, int keep_first, int v_heads) {
   // keep_first (with a window): keys 0 .. keep_first-1 stay visible to every later query.  Those of
   // them that the window has left behind are one more split, behind the num_splits of the window
   // (blockIdx.z == num_splits): the partials have num_splits + 1 places per row then.
@@ -201,7 +204,9 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   pdl_launch_dependents();
   // What follows up to pdl_wait() reads only what the host wrote before the step began (the
   // step's description: starts, positions, block tables) and keys and values of earlier steps.
-  const int entry = blockIdx.x, kv_head = blockIdx.y, split = blockIdx.z;
+  const int entry = blockIdx.x, split = blockIdx.z;
+  const int kv_head = VIRT ? blockIdx.y / v_heads : blockIdx.y;
+  if (VIRT) v_pool += (static_cast<int>(blockIdx.y % v_heads) - kv_head) * D;   // the values of another KV head
   // Token i is entry i in a step of single tokens.  In a step with portions (`entry_starts`
   // given) the entry's token is where its tokens start, and entries that bring more than one
   // token are the flash kernel's.
@@ -331,8 +336,9 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
           weight[w] = m[w] == -INFINITY ? 0.0f : exp2f(m[w] - best);
           total += weight[w] * reinterpret_cast<const float*>(smem + 16 * D * 2 + w * kWarpTile)[row * (D + 4) + D + 1];
         }
-        const int head = kv_head * group + head_in_group;
-        const size_t at = (static_cast<size_t>(entry) * num_heads + head) * places + split;
+        const int head = VIRT ? (kv_head * group + head_in_group) * v_heads + blockIdx.y % v_heads
+                              : kv_head * group + head_in_group;
+        const size_t at = (static_cast<size_t>(entry) * (VIRT ? num_heads * v_heads : num_heads) + head) * places + split;
         if (part == 0) {
           partial_ml[2 * at] = best;
           partial_ml[2 * at + 1] = total;
@@ -799,7 +805,7 @@ int launch_decode(const void* q, void* out, const void* k_pool, const void* v_po
     int status = vipera_launch(attention_decode_kernel<D, true>, grid, 128, kSmem, s,
         static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_pool),
         static_cast<const __nv_bfloat16*>(v_pool), positions, block_table, table_width, page_size, page_shift,
-        num_heads, num_kv_heads, scale, window, chunk, num_splits, partial_ml, partial_out, entry_starts, keep_first);
+        num_heads, num_kv_heads, scale, window, chunk, num_splits, partial_ml, partial_out, entry_starts, keep_first, 0);
     if (status != VIPERA_OK) return status;
     return vipera_launch(attention_combine_kernel<D, true>, dim3(num_entries, num_heads), D, 0, s,
         static_cast<const float*>(partial_ml), static_cast<const float*>(partial_out), num_splits,
@@ -809,11 +815,42 @@ int launch_decode(const void* q, void* out, const void* k_pool, const void* v_po
   int status = vipera_launch(attention_decode_kernel<D>, grid, 128, kSmem, s,
       static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_pool),
       static_cast<const __nv_bfloat16*>(v_pool), positions, block_table, table_width, page_size, page_shift,
-      num_heads, num_kv_heads, scale, window, chunk, num_splits, partial_ml, partial_out, entry_starts, 0);
+      num_heads, num_kv_heads, scale, window, chunk, num_splits, partial_ml, partial_out, entry_starts, 0, 0);
   if (status != VIPERA_OK) return status;
   return vipera_launch(attention_combine_kernel<D>, dim3(num_entries, num_heads), D, 0, s,
       static_cast<const float*>(partial_ml), static_cast<const float*>(partial_out), num_splits,
       static_cast<__nv_bfloat16*>(out), num_heads, positions, window, chunk, entry_starts, 0, 0);
+}
+
+// Single tokens, every query head against every KV head's values: out [entries, heads * kv_heads, D].
+template <int D>
+int launch_decode_pairs(const void* q, void* out, const void* k_pool, const void* v_pool, const int* positions,
+                        const int* block_table, int table_width, int page_size, int num_entries, int num_heads,
+                        int num_kv_heads, float scale, int chunk, int num_splits, float* partial_ml, float* partial_out,
+                        cudaStream_t s) {
+  constexpr int kSmem = 16 * D * 2 + 4 * 2 * 32 * D * 2;
+  int page_shift = -1;
+  if ((page_size & (page_size - 1)) == 0) {
+    page_shift = 0;
+    while ((1 << page_shift) < page_size) ++page_shift;
+  }
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  const int pairs = num_heads * num_kv_heads;
+  dim3 grid(num_entries, num_kv_heads * num_kv_heads, num_splits);
+  int status = vipera_launch(attention_decode_kernel<D, false, true>, grid, 128, kSmem, s,
+      static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_pool),
+      static_cast<const __nv_bfloat16*>(v_pool), positions, block_table, table_width, page_size, page_shift,
+      num_heads, num_kv_heads, scale, 0, chunk, num_splits, partial_ml, partial_out, static_cast<const int*>(nullptr), 0,
+      num_kv_heads);
+  if (status != VIPERA_OK) return status;
+  return vipera_launch(attention_combine_kernel<D>, dim3(num_entries, pairs), D, 0, s,
+      static_cast<const float*>(partial_ml), static_cast<const float*>(partial_out), num_splits,
+      static_cast<__nv_bfloat16*>(out), pairs, positions, 0, chunk, static_cast<const int*>(nullptr), 0, 0);
 }
 
 }  // namespace
@@ -916,6 +953,34 @@ static int run_decode(const void* q, void* out, const void* k_pool, const void* 
     return launch_decode<64>(q, out, k_pool, v_pool, positions, block_table, table_width, page_size, num_entries,
                              num_heads, num_kv_heads, scale, window, chunk, num_splits, partial_ml, partial_out,
                              entry_starts, keep_first, sink, s);
+  return VIPERA_BAD_SHAPE;
+}
+
+// A step of single tokens, every query head against every KV head's values (see
+// vipera_attention_prefill_pairs): out [entries, heads * kv_heads, d]; the scratch is sized for
+// heads * kv_heads heads.
+VIPERA_API int vipera_attention_decode_pairs(const void* q, void* out, const void* k_pool, const void* v_pool,
+                                             const int* positions, const int* block_table, int table_width,
+                                             int page_size, int num_entries, int num_heads, int num_kv_heads,
+                                             int head_dim, float scale, int chunk, int num_splits, float* scratch,
+                                             size_t scratch_floats, void* stream) {
+  if (num_entries <= 0) return VIPERA_OK;
+  if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads) return VIPERA_BAD_SHAPE;
+  if (chunk <= 0 || chunk % 32 || num_splits <= 0 || num_splits > 128) return VIPERA_BAD_ARGUMENT;
+  const int pairs = num_heads * num_kv_heads;
+  if (pairs > 65535 || num_kv_heads * num_kv_heads > 65535) return VIPERA_BAD_SHAPE;
+  const size_t need = vipera_attention_decode_scratch(num_entries, pairs, head_dim, num_splits);
+  if (!scratch || scratch_floats < need || (reinterpret_cast<uintptr_t>(scratch) & 15)) return VIPERA_BAD_ARGUMENT;
+  const size_t rows = static_cast<size_t>(num_entries) * pairs * num_splits;
+  float* partial_ml = scratch;
+  float* partial_out = scratch + ((2 * rows + 3) / 4) * 4;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (head_dim == 128)
+    return launch_decode_pairs<128>(q, out, k_pool, v_pool, positions, block_table, table_width, page_size, num_entries,
+                                    num_heads, num_kv_heads, scale, chunk, num_splits, partial_ml, partial_out, s);
+  if (head_dim == 64)
+    return launch_decode_pairs<64>(q, out, k_pool, v_pool, positions, block_table, table_width, page_size, num_entries,
+                                   num_heads, num_kv_heads, scale, chunk, num_splits, partial_ml, partial_out, s);
   return VIPERA_BAD_SHAPE;
 }
 

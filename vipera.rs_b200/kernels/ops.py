@@ -1223,6 +1223,35 @@ def attention_talk_prefill(q: torch.Tensor, out: torch.Tensor, pairs: torch.Tens
               num_kv_heads, head_dim, float(out_scale), _stream()), "attention")
 
 
+def attention_talk_decode(q: torch.Tensor, out: torch.Tensor, pairs: torch.Tensor, k_pool: torch.Tensor,
+                          v_pool: torch.Tensor, mix: torch.Tensor, *, positions: torch.Tensor, block_table: torch.Tensor,
+                          num_heads: int, num_kv_heads: int, head_dim: int, scale: float, chunk: int, num_splits: int,
+                          scratch: torch.Tensor, out_scale: float = 1.0) -> None:
+    """``attention_talk_prefill`` for a step of single tokens: the split-key kernel computes every
+    (query head, KV head) pair into ``pairs`` [entries, heads * kv_heads * d] (``chunk``, ``num_splits``
+    and ``scratch`` as for ``attention_decode``, the scratch sized for heads * kv_heads heads), then
+    the mix of the pairs' outputs."""
+    if head_dim not in MMA_HEAD_DIMS:
+        raise UnsupportedError(f"attention_talk_decode: head size {head_dim} (built: 64, 128)")
+    count = q.shape[0]
+    if q.shape[1] != num_heads * head_dim or out.shape != q.shape or \
+            tuple(pairs.shape) != (count, num_heads * num_kv_heads * head_dim) or positions.numel() != count:
+        raise InvalidArgumentError("attention_talk_decode: q and out must be [entries, heads * d], pairs [entries, heads * kv_heads * d]")
+    if k_pool.shape[2:] != (num_kv_heads, head_dim) or v_pool.shape != k_pool.shape:
+        raise InvalidArgumentError("attention_talk_decode: cache pools must be [pages, page_size, kv_heads, d]")
+    fn = _function("attention_mma", "vipera_attention_decode_pairs",
+                   [_c_void] * 6 + [_c_int] * 6 + [_c_float, _c_int, _c_int, _c_void, ctypes.c_size_t, _c_void])
+    _check(fn(_gpu(q, "q", torch.bfloat16), _gpu(pairs, "pairs", torch.bfloat16), _gpu(k_pool, "k_pool", torch.bfloat16),
+              _gpu(v_pool, "v_pool", torch.bfloat16), _gpu(positions, "positions", torch.int32),
+              _gpu(block_table, "block_table", torch.int32), block_table.shape[1], k_pool.shape[1], count, num_heads,
+              num_kv_heads, head_dim, float(scale), int(chunk), int(num_splits), _gpu(scratch, "scratch", torch.float32),
+              scratch.numel(), _stream()), "attention_decode", kernels=2)
+    fn = _function("attention_talk", "vipera_talk_combine",
+                   [_c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void])
+    _check(fn(pairs.data_ptr(), _gpu(mix, "mix", torch.float32), _gpu(out, "out", torch.bfloat16), BF16, count, num_heads,
+              num_kv_heads, head_dim, float(out_scale), _stream()), "attention")
+
+
 # ----------------------------------------------------------------------------------------
 # recurrences with a state of fixed size: Mamba's selective scan, gated linear attention
 # ----------------------------------------------------------------------------------------

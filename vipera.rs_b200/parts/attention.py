@@ -244,8 +244,23 @@ class GQAttention(Mixer):
         window = self.window or 0
         if self.talk is not None:
             count = ctx.num_tokens
-            if (not ctx.all_single and ctx.dtype == torch.bfloat16 and d in ops.MMA_HEAD_DIMS and self.value_dim == d
-                    and count >= self.TALK_PAIRS_FROM and heads * kv_heads <= 4096):
+            tensor_cores = (ctx.dtype == torch.bfloat16 and d in ops.MMA_HEAD_DIMS and self.value_dim == d
+                            and heads * kv_heads <= 4096 and os.environ.get("VIPERA_TALK_PAIRS", "1") != "0")
+            if ctx.all_single and tensor_cores:
+                # single tokens: the same pairs through the split-key kernel, which streams the history
+                # through shared memory once per pair of KV heads
+                chunk, splits = ops.decode_splits(ctx.num_entries, kv_heads * kv_heads, max(ctx.max_kv_len, 1),
+                                                  ops.sm_count(q.device))
+                scratch = ctx.workspace.get(
+                    "attention.partials",
+                    (ops.attention_decode_scratch_floats(ctx.num_entries, heads * kv_heads, d, splits),), torch.float32)
+                pairs = ctx.workspace.get("attention.talk_pairs", (count, heads * kv_heads * d), ctx.dtype)
+                ops.attention_talk_decode(q, mixed, pairs, cache.k, cache.v, self.talk, positions=ctx.positions,
+                                          block_table=table, num_heads=heads, num_kv_heads=kv_heads, head_dim=d,
+                                          scale=self.scale, chunk=chunk, num_splits=splits, scratch=scratch,
+                                          out_scale=self.out_scale)
+                return
+            if not ctx.all_single and tensor_cores and count >= self.TALK_PAIRS_FROM:
                 # steps with portions on the tensor cores: every (query head, KV head) pair through the
                 # flash kernel, then the mix of the pairs' outputs
                 pairs = ctx.workspace.get("attention.talk_pairs", (count, heads * kv_heads * d), ctx.dtype)
