@@ -11,11 +11,11 @@
 // carried from portion to portion.  Decays (through log sigmoid), state, products with the state
 // and the norm are 32-bit.
 //
-// gla_scan_kernel: a block owns (a tile of 32 value columns, head, entry); warp r of the block
-// holds rows r*ROWS .. r*ROWS+ROWS-1 of the tile's columns in registers (a lane a column) and
-// walks the entry's tokens in order.  Each warp writes its share of o to a scratch
-// [row shares][tokens][heads*dv]; gla_finish_kernel adds the shares in a fixed order and applies
-// norm, gate and scale (a warp per (token, head)).
+// gla_decay_kernel forms the decays and their logarithms once per token and key channel.
+// gla_scan_kernel: a block owns (ROWS rows of the state: a "share", up to eight tiles of 32 value
+// columns, head, entry or chunk) and walks the tokens in order (see there).  Each share writes its
+// part of o to a scratch [row shares][tokens][heads*dv]; gla_finish_kernel adds the shares in a
+// fixed order and applies norm, gate and scale (a warp per (token, head)).
 //
 // Long steps are cut into chunks of kGlaChunk tokens that run side by side, in three launches:
 // every chunk from a zero state (its end state E and, per key channel, the sum of its log decays,
@@ -83,18 +83,28 @@ __global__ void __launch_bounds__(256) gla_decay_kernel(const GlaParams p) {
   }
 }
 
+constexpr int kGlaTile = 64;      // tokens whose decays, keys and queries a block stages at a time
+constexpr int kGlaWarps = 8;      // value tiles (of 32 columns) a block covers
+
+// A block owns ROWS rows of a head's state (a "share") for up to kGlaWarps tiles of 32 value
+// columns: a warp a tile, a lane a column, the rows in registers.  The rows' decays, keys and
+// scaled queries of kGlaTile tokens at a time are staged in shared memory by the whole block (they
+// are the same for every column); a token then costs a warp one coalesced load of v, broadcast
+// reads of the staged rows, and 2 * ROWS multiply-adds.
 template <int ROWS>
-__global__ void __launch_bounds__(kGlaMaxShares * 32) gla_scan_kernel(const GlaParams p) {
+__global__ void __launch_bounds__(kGlaWarps * 32) gla_scan_kernel(const GlaParams p) {
+  __shared__ __align__(16) float staged[3][kGlaTile][ROWS];   // decays, keys, queries
   pdl_launch_dependents();
-  const int lane = threadIdx.x & 31, share = threadIdx.x >> 5;
-  const int column = blockIdx.x * 32 + lane;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int share = blockIdx.x % p.shares, tiles0 = (blockIdx.x / p.shares) * kGlaWarps;
+  const int column = (tiles0 + warp) * 32 + lane;
   const int head = blockIdx.y;
   int entry = blockIdx.z;
   const bool live = column < p.vdim;
   const int row0 = share * ROWS;
-  float s[ROWS], log_decay[ROWS];
+  float s[ROWS];
 #pragma unroll
-  for (int r = 0; r < ROWS; ++r) s[r] = log_decay[r] = 0.0f;
+  for (int r = 0; r < ROWS; ++r) s[r] = 0.0f;
   pdl_wait();
   int first, last;
   float* state;
@@ -117,34 +127,52 @@ __global__ void __launch_bounds__(kGlaMaxShares * 32) gla_scan_kernel(const GlaP
   }
   const size_t out_width = static_cast<size_t>(p.heads) * p.vdim;
   float* partial = p.partial + static_cast<size_t>(share) * p.num_tokens * out_width + head * p.vdim;
-  for (int t = first; t < last; ++t) {
-    const float* row = p.proj + static_cast<size_t>(t) * p.proj_width;
-    const float* q = row + p.q_off + head * p.dim + row0;
-    const float* k = row + p.k_off + head * p.dim + row0;
-    const size_t decay_at = (static_cast<size_t>(t) * p.heads + head) * p.dim + row0;
-    const float* alpha = p.z + decay_at;
-    const float v = live ? row[p.v_off + head * p.vdim + column] : 0.0f;
-    float o = 0.0f;
-#pragma unroll
-    for (int r = 0; r < ROWS; ++r) {
-      if (row0 + r < p.dim) {
-        if (p.mode == 1) log_decay[r] += p.log_alpha[decay_at + r];
-        s[r] = fmaf(alpha[r], s[r], k[r] * v);
-        o = fmaf(s[r], q[r] * p.q_scale, o);
-      }
+  const float* v_column = p.proj + p.v_off + head * p.vdim + (live ? column : 0);
+  for (int t0 = first; t0 < last; t0 += kGlaTile) {
+    const int count = min(kGlaTile, last - t0);
+    __syncthreads();
+    for (int index = threadIdx.x; index < count * ROWS; index += blockDim.x) {
+      const int tt = index / ROWS, r = index % ROWS;
+      const bool valid = row0 + r < p.dim;
+      const float* row = p.proj + static_cast<size_t>(t0 + tt) * p.proj_width + head * p.dim + row0 + r;
+      staged[0][tt][r] = valid ? p.z[(static_cast<size_t>(t0 + tt) * p.heads + head) * p.dim + row0 + r] : 0.0f;
+      staged[1][tt][r] = valid ? row[p.k_off] : 0.0f;
+      staged[2][tt][r] = valid ? row[p.q_off] * p.q_scale : 0.0f;
     }
-    if (live && p.mode != 1) partial[static_cast<size_t>(t) * out_width + column] = o;
+    __syncthreads();
+    float v_next = v_column[static_cast<size_t>(t0) * p.proj_width];
+    for (int tt = 0; tt < count; ++tt) {
+      const float v = live ? v_next : 0.0f;
+      if (tt + 1 < count) v_next = v_column[static_cast<size_t>(t0 + tt + 1) * p.proj_width];
+      float o = 0.0f;
+#pragma unroll
+      for (int r = 0; r < ROWS; r += 4) {
+        const float4 alpha = *reinterpret_cast<const float4*>(&staged[0][tt][r]);
+        const float4 k = *reinterpret_cast<const float4*>(&staged[1][tt][r]);
+        const float4 q = *reinterpret_cast<const float4*>(&staged[2][tt][r]);
+        s[r] = fmaf(alpha.x, s[r], k.x * v);
+        o = fmaf(s[r], q.x, o);
+        s[r + 1] = fmaf(alpha.y, s[r + 1], k.y * v);
+        o = fmaf(s[r + 1], q.y, o);
+        s[r + 2] = fmaf(alpha.z, s[r + 2], k.z * v);
+        o = fmaf(s[r + 2], q.z, o);
+        s[r + 3] = fmaf(alpha.w, s[r + 3], k.w * v);
+        o = fmaf(s[r + 3], q.w, o);
+      }
+      if (live && p.mode != 1) partial[static_cast<size_t>(t0 + tt) * out_width + column] = o;
+    }
   }
   if (live && p.mode != 3) {
 #pragma unroll
     for (int r = 0; r < ROWS; ++r)
       if (row0 + r < p.dim) state[static_cast<size_t>(row0 + r) * p.vdim + column] = s[r];
   }
-  if (p.mode == 1 && blockIdx.x == 0 && lane == 0) {
-#pragma unroll
-    for (int r = 0; r < ROWS; ++r)
-      if (row0 + r < p.dim)
-        p.chunk_decay[(static_cast<size_t>(blockIdx.z) * p.heads + head) * p.dim + row0 + r] = log_decay[r];
+  if (p.mode == 1 && blockIdx.x < p.shares && threadIdx.x < ROWS && row0 + threadIdx.x < p.dim) {
+    // the chunk's whole decay per key channel: the sum of its log decays, in token order
+    float sum = 0.0f;
+    for (int t = first; t < last; ++t)
+      sum += p.log_alpha[(static_cast<size_t>(t) * p.heads + head) * p.dim + row0 + threadIdx.x];
+    p.chunk_decay[(static_cast<size_t>(blockIdx.z) * p.heads + head) * p.dim + row0 + threadIdx.x] = sum;
   }
 }
 
@@ -218,10 +246,12 @@ VIPERA_API int vipera_gla(const GlaParams* params, int out_dtype, void* stream) 
   const bool chunked = p.num_jobs > 0 && p.chunk_state && p.chunk_decay;
   auto pass = [&](int mode) -> int {
     p.mode = mode;
-    dim3 grid((p.vdim + 31) / 32, p.heads, mode == 0 ? p.num_entries : p.num_jobs);
-    if (rows == 8) return vipera_launch(gla_scan_kernel<8>, grid, p.shares * 32, 0, s, p);
-    if (rows == 16) return vipera_launch(gla_scan_kernel<16>, grid, p.shares * 32, 0, s, p);
-    return vipera_launch(gla_scan_kernel<32>, grid, p.shares * 32, 0, s, p);
+    const int tiles = (p.vdim + 31) / 32;
+    const int warps = std::min(tiles, kGlaWarps);
+    dim3 grid(p.shares * ((tiles + kGlaWarps - 1) / kGlaWarps), p.heads, mode == 0 ? p.num_entries : p.num_jobs);
+    if (rows == 8) return vipera_launch(gla_scan_kernel<8>, grid, warps * 32, 0, s, p);
+    if (rows == 16) return vipera_launch(gla_scan_kernel<16>, grid, warps * 32, 0, s, p);
+    return vipera_launch(gla_scan_kernel<32>, grid, warps * 32, 0, s, p);
   };
   const size_t decays = static_cast<size_t>(p.num_tokens) * p.heads * p.dim;
   int status = vipera_launch(gla_decay_kernel, dim3(static_cast<unsigned>(std::min<size_t>((decays + 255) / 256, 4096))), 256, 0, s, p);

@@ -23,6 +23,8 @@
 // re-associates 32-bit sums.  Chunks are counted from where an entry's tokens start in the step.
 #include "common.cuh"
 
+#include <algorithm>
+
 constexpr int kScanThreads = 128;
 
 struct ScanParams {
@@ -66,14 +68,25 @@ __device__ __forceinline__ bool scan_job(const int* __restrict__ entry_starts, i
   return false;
 }
 
+// Tokens are staged in shared memory `tile` at a time by the whole block: the step sizes (softplus
+// applied once per token and channel), x and the gate of the block's channels, and the B and C
+// rows; the walk over the tokens then reads shared memory only.
 template <typename TO, int NPL>
-__global__ void __launch_bounds__(kScanThreads) mamba_scan_kernel(const ScanParams p) {
+__global__ void __launch_bounds__(kScanThreads) mamba_scan_kernel(const ScanParams p, int tile) {
+  extern __shared__ __align__(16) float staged[];
   pdl_launch_dependents();
   const int lanes = p.lanes;
+  const int per_block = kScanThreads / lanes;               // channels of a block
   const int sub = threadIdx.x % lanes;                      // which share of the states
-  const int c = (blockIdx.x * kScanThreads + threadIdx.x) / lanes;
+  const int local = threadIdx.x / lanes;
+  const int c0 = blockIdx.x * per_block;
+  const int c = c0 + local;
   const bool live = c < p.channels;
   int entry = blockIdx.y;
+  float* dt_s = staged;                                     // [tile][per_block]
+  float* x_s = dt_s + tile * per_block;
+  float* z_s = x_s + tile * per_block;
+  float* bc_s = z_s + tile * per_block;                     // [tile][2 * states]
   float a[NPL], s[NPL];
 #pragma unroll
   for (int j = 0; j < NPL; ++j) {
@@ -105,31 +118,46 @@ __global__ void __launch_bounds__(kScanThreads) mamba_scan_kernel(const ScanPara
     }
   }
   TO* out = static_cast<TO*>(p.out);
-  const int cc = live ? c : 0;
   float dt_sum = 0.0f;
-  for (int t = first; t < last; ++t) {
-    const float pre = p.dt_pre[static_cast<size_t>(t) * p.channels + cc];
-    const float x = p.x[static_cast<size_t>(t) * p.channels + cc];
-    const float dt = pre > 20.0f ? pre : log1pf(expf(pre));
-    const float* b_row = p.bc + static_cast<size_t>(t) * 2 * p.states;
-    const float* c_row = b_row + p.states;
-    const float dtx = dt * x;
-    dt_sum += dt;
-    float y = 0.0f;
-#pragma unroll
-    for (int j = 0; j < NPL; ++j) {
-      const int n = sub * NPL + j;
-      if (n < p.states) {
-        s[j] = fmaf(expf(dt * a[j]), s[j], dtx * b_row[n]);
-        y = fmaf(s[j], c_row[n], y);
-      }
+  const int width = 2 * p.states;
+  for (int t0 = first; t0 < last; t0 += tile) {
+    const int count = min(tile, last - t0);
+    __syncthreads();
+    for (int index = threadIdx.x; index < count * per_block; index += kScanThreads) {
+      const int tt = index / per_block, cl = index % per_block;
+      const bool valid = c0 + cl < p.channels;
+      const size_t at = static_cast<size_t>(t0 + tt) * p.channels + c0 + cl;
+      const float pre = valid ? p.dt_pre[at] : 0.0f;
+      dt_s[index] = pre > 20.0f ? pre : log1pf(expf(pre));
+      x_s[index] = valid ? p.x[at] : 0.0f;
+      z_s[index] = (valid && p.mode != 1) ? p.z[static_cast<size_t>(t0 + tt) * p.z_stride + p.z_offset + c0 + cl] : 0.0f;
     }
-    if (p.mode == 1) continue;   // the pass that only finds the chunks' end states
-    for (int offset = lanes >> 1; offset > 0; offset >>= 1) y += __shfl_xor_sync(0xffffffffu, y, offset);
-    if (live && sub == 0) {
-      const float gate = p.z[static_cast<size_t>(t) * p.z_stride + p.z_offset + c];
-      y = fmaf(skip, x, y);
-      out[static_cast<size_t>(t) * p.channels + c] = from_float<TO>(y * (gate / (1.0f + expf(-gate))));
+    for (int index = threadIdx.x; index < count * width; index += kScanThreads)
+      bc_s[index] = p.bc[static_cast<size_t>(t0) * width + index];
+    __syncthreads();
+    for (int tt = 0; tt < count; ++tt) {
+      const float dt = dt_s[tt * per_block + local];
+      const float x = x_s[tt * per_block + local];
+      const float* b_row = bc_s + tt * width;
+      const float* c_row = b_row + p.states;
+      const float dtx = dt * x;
+      dt_sum += dt;
+      float y = 0.0f;
+#pragma unroll
+      for (int j = 0; j < NPL; ++j) {
+        const int n = sub * NPL + j;
+        if (n < p.states) {
+          s[j] = fmaf(expf(dt * a[j]), s[j], dtx * b_row[n]);
+          y = fmaf(s[j], c_row[n], y);
+        }
+      }
+      if (p.mode == 1) continue;   // the pass that only finds the chunks' end states
+      for (int offset = lanes >> 1; offset > 0; offset >>= 1) y += __shfl_xor_sync(0xffffffffu, y, offset);
+      if (live && sub == 0) {
+        const float gate = z_s[tt * per_block + local];
+        y = fmaf(skip, x, y);
+        out[static_cast<size_t>(t0 + tt) * p.channels + c] = from_float<TO>(y * (gate / (1.0f + expf(-gate))));
+      }
     }
   }
   if (live && p.mode != 3) {
@@ -191,13 +219,18 @@ VIPERA_API int vipera_mamba_scan(const ScanParams* params, int out_dtype, void* 
   const bool chunked = p.num_jobs > 0 && p.chunk_state && p.chunk_dt;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (out_dtype != VIPERA_BF16 && out_dtype != VIPERA_F32) return VIPERA_BAD_DTYPE;
+  // tokens staged at a time: what fits 40 KB beside the block's channels, at most a chunk
+  const size_t per_token = (3 * static_cast<size_t>(channels_per_block) + 2 * p.states) * sizeof(float);
+  const int tile = static_cast<int>(std::max<size_t>(1, std::min<size_t>(kScanChunk, (40 * 1024) / per_token)));
+  const size_t shared_bytes = tile * per_token;
   auto pass = [&](int mode) -> int {
     p.mode = mode;
     dim3 grid((p.channels + channels_per_block - 1) / channels_per_block, mode == 0 ? p.num_entries : p.num_jobs);
 #define SCAN_CASE(N)                                                                                     \
   if (per_lane == N) {                                                                                   \
-    if (out_dtype == VIPERA_BF16) return vipera_launch(mamba_scan_kernel<__nv_bfloat16, N>, grid, kScanThreads, 0, s, p); \
-    return vipera_launch(mamba_scan_kernel<float, N>, grid, kScanThreads, 0, s, p);                       \
+    if (out_dtype == VIPERA_BF16)                                                                        \
+      return vipera_launch(mamba_scan_kernel<__nv_bfloat16, N>, grid, kScanThreads, shared_bytes, s, p, tile); \
+    return vipera_launch(mamba_scan_kernel<float, N>, grid, kScanThreads, shared_bytes, s, p, tile);       \
   }
     SCAN_CASE(1) SCAN_CASE(2) SCAN_CASE(4) SCAN_CASE(8) SCAN_CASE(16)
 #undef SCAN_CASE
