@@ -174,3 +174,14 @@ def test_the_plain_model_depends_on_every_edge_the_gpu_tests_rely_on():
     changed[3] = (changed[3] + 1) % config["vocab"]
     moved = plain.forward(config, weights, changed).numpy()
     assert np.abs(moved[-20:] - base[-20:]).max() / np.abs(base).max() > 1e-3
+
+
+def test_a_file_may_hold_the_second_sublayer_of_a_layer_without_feed_forward():
+    from vipera_rs_b200.config.gusolix import gusolix_ignorable
+
+    arch, _ = spec_of("mixed")
+    config = arch.config_from_dict(cases.MIXED)
+    assert gusolix_ignorable(config, "l1.norm2.weight") and gusolix_ignorable(config, "l1.canon2.weight")
+    assert gusolix_ignorable(config, "l1.norm2.bias")
+    assert not gusolix_ignorable(config, "l0.norm2.weight") and not gusolix_ignorable(config, "l1.norm1.weight")
+    assert not gusolix_ignorable(config, "l9.norm2.weight") and not gusolix_ignorable(config, "l1.mix.q.weight")

@@ -18,6 +18,7 @@ names in the weight file: ``embed``, ``l<i>.norm1``, ``l<i>.canon1``, ``l<i>.mix
 """
 from __future__ import annotations
 
+import re
 from dataclasses import dataclass, field
 from typing import Any, Dict, List, Optional, Tuple
 
@@ -242,5 +243,15 @@ def gusolix_model_spec(config: GusolixConfig) -> ModelSpec:
     return spec
 
 
+_SECOND_SUBLAYER = re.compile(r"^l(\d+)\.(norm2\.(weight|bias)|canon2\.weight)$")
+
+
+def gusolix_ignorable(config: GusolixConfig, name: str) -> bool:
+    """A file may hold the second sublayer's norm and filter for a layer without a feed-forward;
+    nothing reads them."""
+    match = _SECOND_SUBLAYER.match(name)
+    return bool(match) and int(match.group(1)) < len(config.layers) and config.layers[int(match.group(1))].ff is None
+
+
 register_architecture("Gusolix", GusolixConfig.from_dict, gusolix_model_spec,
-                      tensor_alias=nobupel_tensor_alias, stored_name=nobupel_stored_name)
+                      tensor_alias=nobupel_tensor_alias, stored_name=nobupel_stored_name, ignorable=gusolix_ignorable)

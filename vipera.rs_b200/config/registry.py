@@ -66,6 +66,10 @@ class Architecture:
     # The inverse where the architecture's own files use other names than the parts:
     # ``stored_name(name_a_part_asks_for)`` is the name a written weight file stores it under.
     stored_name: Optional[Callable[[str], str]] = None
+    # Tensors a weight file may hold although the model does not read them:
+    # ``ignorable(config, name_a_part_would_ask_for)`` is true for those; they are left out of
+    # the check for unexpected tensors.
+    ignorable: Optional[Callable[[Any, str], bool]] = None
 
 
 ARCHITECTURES: Registry[Architecture] = Registry("architecture")
@@ -77,7 +81,7 @@ BLOCKS: Registry[type] = Registry("block arrangement")
 
 
 def register_architecture(name, config_from_dict, model_spec, *, tensor_alias=None, stored_name=None,
-                          replace=False) -> Architecture:
+                          ignorable=None, replace=False) -> Architecture:
     return ARCHITECTURES.register(
-        name, Architecture(name, config_from_dict, model_spec, tensor_alias, stored_name), replace=replace
+        name, Architecture(name, config_from_dict, model_spec, tensor_alias, stored_name, ignorable), replace=replace
     )

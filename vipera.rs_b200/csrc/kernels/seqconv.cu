@@ -12,7 +12,7 @@
 // step's own rows: the "segment" jobs.  An entry without tokens leaves its state alone.
 #include "common.cuh"
 
-constexpr int kConvMaxTaps = 8;
+constexpr int kConvMaxTaps = 16;
 constexpr int kConvThreads = 128;
 constexpr int kConvSegment = 8;   // tokens of a segment job
 

@@ -11,7 +11,7 @@ from ..build import build_kernels
 from ..config import architecture_of, load_config, read_config_json
 from ..errors import InvalidArgumentError
 from ..parts.model import DecoderModel, model_schema
-from ..weights import AliasedSource, RandomSource, SafetensorsSource, write_model_folder
+from ..weights import AliasedSource, RandomSource, SafetensorsSource, SourceWithout, write_model_folder
 
 
 def _kernel_families(model) -> list:
@@ -42,6 +42,9 @@ def load_model(model_dir: str, dtype="bfloat16", device="cuda:0") -> DecoderMode
     source = SafetensorsSource(model_dir)
     if arch.tensor_alias is not None:
         source = AliasedSource(source, arch.tensor_alias)
+    if arch.ignorable is not None:
+        wanted = model_schema(spec)
+        source = SourceWithout(source, lambda name: name not in wanted and arch.ignorable(config, name))
     model = DecoderModel(spec, source, parse_dtype(dtype), device)
     model.config = config
     build_kernels(_kernel_families(model))

@@ -1031,7 +1031,7 @@ def layernorm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, out: to
 
 CONV_ACT_NONE, CONV_ACT_SILU = 0, 1
 CONV_ACTIVATIONS = {"none": CONV_ACT_NONE, "silu": CONV_ACT_SILU}
-CONV_MAX_TAPS = 8
+CONV_MAX_TAPS = 16
 
 
 class _ConvParams(ctypes.Structure):

@@ -4,6 +4,7 @@ from .loader import (
     INIT,
     RandomSource,
     SafetensorsSource,
+    SourceWithout,
     Schema,
     TensorSpec,
     WeightSource,
@@ -14,6 +15,6 @@ from .loader import (
 from .safetensors_io import SafetensorsFile, write_safetensors
 
 __all__ = [
-    "AliasedSource", "INIT", "RandomSource", "SafetensorsSource", "Schema", "TensorSpec", "WeightSource",
+    "AliasedSource", "INIT", "RandomSource", "SafetensorsSource", "SourceWithout", "Schema", "TensorSpec", "WeightSource",
     "check_source", "to_run_dtype", "write_model_folder", "SafetensorsFile", "write_safetensors",
 ]

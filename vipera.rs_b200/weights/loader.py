@@ -146,6 +146,29 @@ class AliasedSource(WeightSource):
         return self._source.describe()
 
 
+class SourceWithout(WeightSource):
+    """A source that hides the tensors ``hidden(name)`` is true for."""
+
+    def __init__(self, source: WeightSource, hidden):
+        self._source = source
+        self._names = [name for name in source.names() if not hidden(name)]
+
+    def names(self) -> List[str]:
+        return list(self._names)
+
+    def shape(self, name: str) -> Tuple[int, ...]:
+        return self._source.shape(name)
+
+    def stored_dtype(self, name: str) -> torch.dtype:
+        return self._source.stored_dtype(name)
+
+    def get(self, name: str) -> torch.Tensor:
+        return self._source.get(name)
+
+    def describe(self) -> str:
+        return self._source.describe()
+
+
 def _fnv1a64(text: str) -> int:
     value = 0xCBF29CE484222325
     for byte in text.encode("utf-8"):
