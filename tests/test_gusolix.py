@@ -185,3 +185,18 @@ def test_a_file_may_hold_the_second_sublayer_of_a_layer_without_feed_forward():
     assert gusolix_ignorable(config, "l1.norm2.bias")
     assert not gusolix_ignorable(config, "l0.norm2.weight") and not gusolix_ignorable(config, "l1.norm1.weight")
     assert not gusolix_ignorable(config, "l9.norm2.weight") and not gusolix_ignorable(config, "l1.mix.q.weight")
+
+
+def test_the_cut_of_the_mixed_weights_attention_covers_every_history():
+    from vipera_rs_b200.kernels import ops
+
+    for tokens in (1, 2, 7, 8, 64, 300, 5000):
+        for max_keys in (1, 31, 32, 33, 64, 65, 1000, 2048, 2049, 100000):
+            keys, splits = ops.talk_splits(tokens, max_keys, 148)
+            assert keys % 32 == 0 and keys >= 32 and splits >= 1
+            assert keys * splits >= max_keys > keys * (splits - 1)
+            if tokens >= 296:
+                assert splits == 1
+    # chunks of a step: an entry more than whole chunks of all tokens bounds them
+    for tokens, entries in ((1, 1), (64, 1), (65, 2), (2048, 5)):
+        assert ops.scan_jobs(tokens, entries) >= sum(-(-n // ops.SCAN_CHUNK) for n in [tokens - entries + 1] + [1] * (entries - 1))
