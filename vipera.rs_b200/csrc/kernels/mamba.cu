@@ -127,6 +127,7 @@ __global__ void __launch_bounds__(kScanThreads) mamba_scan_kernel(const ScanPara
   TO* out = static_cast<TO*>(p.out);
   float dt_sum = 0.0f;
   const int width = 2 * p.states;
+  const bool vector_rows = (p.states & 3) == 0 && ((3 * tile * per_block) & 3) == 0;
   for (int t0 = first; t0 < last; t0 += tile) {
     const int count = min(tile, last - t0);
     __syncthreads();
@@ -150,12 +151,28 @@ __global__ void __launch_bounds__(kScanThreads) mamba_scan_kernel(const ScanPara
       const float dtx = dt * x;
       dt_sum += dt;
       float y = 0.0f;
+      if (NPL == 4 && vector_rows) {
+        // four states a lane, rows of B and C that start on 16 bytes: one read each
+        if (sub * 4 < p.states) {
+          const float4 b4 = *reinterpret_cast<const float4*>(b_row + sub * 4);
+          const float4 c4 = *reinterpret_cast<const float4*>(c_row + sub * 4);
+          s[0] = fmaf(scan_exp<TO>(dt * a[0]), s[0], dtx * b4.x);
+          y = fmaf(s[0], c4.x, y);
+          s[1 % NPL] = fmaf(scan_exp<TO>(dt * a[1 % NPL]), s[1 % NPL], dtx * b4.y);
+          y = fmaf(s[1 % NPL], c4.y, y);
+          s[2 % NPL] = fmaf(scan_exp<TO>(dt * a[2 % NPL]), s[2 % NPL], dtx * b4.z);
+          y = fmaf(s[2 % NPL], c4.z, y);
+          s[3 % NPL] = fmaf(scan_exp<TO>(dt * a[3 % NPL]), s[3 % NPL], dtx * b4.w);
+          y = fmaf(s[3 % NPL], c4.w, y);
+        }
+      } else {
 #pragma unroll
-      for (int j = 0; j < NPL; ++j) {
-        const int n = sub * NPL + j;
-        if (n < p.states) {
-          s[j] = fmaf(scan_exp<TO>(dt * a[j]), s[j], dtx * b_row[n]);
-          y = fmaf(s[j], c_row[n], y);
+        for (int j = 0; j < NPL; ++j) {
+          const int n = sub * NPL + j;
+          if (n < p.states) {
+            s[j] = fmaf(scan_exp<TO>(dt * a[j]), s[j], dtx * b_row[n]);
+            y = fmaf(s[j], c_row[n], y);
+          }
         }
       }
       if (p.mode == 1) continue;   // the pass that only finds the chunks' end states
@@ -228,9 +245,10 @@ VIPERA_API int vipera_mamba_scan(const ScanParams* params, int out_dtype, void* 
   const int channels_per_block = kScanThreads / p.lanes;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (out_dtype != VIPERA_BF16 && out_dtype != VIPERA_F32) return VIPERA_BAD_DTYPE;
-  // tokens staged at a time: what fits 40 KB beside the block's channels, at most a chunk
+  // tokens staged at a time: what fits 16 KB beside the block's channels (so that an SM holds a
+  // dozen blocks), at most half a chunk
   const size_t per_token = (3 * static_cast<size_t>(channels_per_block) + 2 * p.states) * sizeof(float);
-  const int tile = static_cast<int>(std::max<size_t>(1, std::min<size_t>(kScanChunk, (40 * 1024) / per_token)));
+  const int tile = static_cast<int>(std::max<size_t>(1, std::min<size_t>(kScanChunk / 2, (16 * 1024) / per_token)));
   const size_t shared_bytes = tile * per_token;
   auto pass = [&](int mode) -> int {
     p.mode = mode;
