@@ -67,7 +67,7 @@ ODD = config([attention_layer(heads=1, kv_heads=1, dim=18, scale=0.7, size=1000,
               attention_layer(heads=6, kv_heads=3, dim=8, scale=1.0, size=1, rot_dims=2, scaling=False, ff=20),
               mamba_layer(inner=24, state=37, dt_rank=9, conv=5, ff=16)],
              width=100, vocab=97, eps=1e-4, taps=1, scale=1.0)
-LONG_TAPS = config([mamba_layer(inner=48, state=8, dt_rank=4, conv=7, ff=32), parallel_layer()], width=64, taps=6)
+LONG_TAPS = config([mamba_layer(inner=48, state=8, dt_rank=4, conv=7, ff=32), parallel_layer()], width=64, taps=11)
 ONLY_ATTENTION = config([attention_layer()])
 ONLY_MAMBA = config([mamba_layer()])
 ONLY_PARALLEL = config([parallel_layer()])

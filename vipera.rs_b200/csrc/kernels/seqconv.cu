@@ -50,15 +50,16 @@ __device__ __forceinline__ void conv_store(const ConvParams& p, int t, int c, fl
   if (p.clear) p.clear[at] = 0.0f;
 }
 
-template <typename TO>
+// MAXT: the most taps this instance takes (its register arrays and unrolled loops are that long).
+template <typename TO, int MAXT>
 __global__ void __launch_bounds__(kConvThreads) causal_conv_kernel(const ConvParams p) {
   pdl_launch_dependents();
   const int c = blockIdx.x * kConvThreads + threadIdx.x;
   const bool live = c < p.channels;
   const int taps = p.taps;
-  float w[kConvMaxTaps];
+  float w[MAXT];
 #pragma unroll
-  for (int j = 0; j < kConvMaxTaps; ++j) w[j] = (live && j < taps) ? p.weight[static_cast<size_t>(c) * taps + j] : 0.0f;
+  for (int j = 0; j < MAXT; ++j) w[j] = (live && j < taps) ? p.weight[static_cast<size_t>(c) * taps + j] : 0.0f;
   const float bias = (live && p.bias) ? p.bias[c] : 0.0f;
   pdl_wait();
   if (!live) return;
@@ -67,15 +68,15 @@ __global__ void __launch_bounds__(kConvThreads) causal_conv_kernel(const ConvPar
     // head job: the entry's first taps - 1 tokens and its new state
     const int first = p.entry_starts[job], count = p.entry_starts[job + 1] - first;
     if (count <= 0) return;
-    float old[kConvMaxTaps];   // old[k], k < taps - 1: the input at in-entry index k - (taps - 1)
+    float old[MAXT];   // old[k], k < taps - 1: the input at in-entry index k - (taps - 1)
 #pragma unroll
-    for (int k = 0; k < kConvMaxTaps; ++k) old[k] = 0.0f;
+    for (int k = 0; k < MAXT; ++k) old[k] = 0.0f;
     float* state = nullptr;
     if (p.state && taps > 1) {
       state = p.state + static_cast<size_t>(p.state_slots[job]) * p.state_stride;
       if (!p.fresh[job]) {
 #pragma unroll
-        for (int k = 0; k < kConvMaxTaps - 1; ++k)
+        for (int k = 0; k < MAXT - 1; ++k)
           if (k < taps - 1) old[k] = state[static_cast<size_t>(k) * p.channels + c];
       }
     }
@@ -83,7 +84,7 @@ __global__ void __launch_bounds__(kConvThreads) causal_conv_kernel(const ConvPar
     for (int i = 0; i < heads; ++i) {
       float sum = 0.0f, current = 0.0f;
 #pragma unroll
-      for (int j = 0; j < kConvMaxTaps; ++j) {
+      for (int j = 0; j < MAXT; ++j) {
         if (j < taps) {
           const int index = i - (taps - 1) + j;   // in-entry index of the input
           float value;
@@ -91,7 +92,7 @@ __global__ void __launch_bounds__(kConvThreads) causal_conv_kernel(const ConvPar
           else {
             value = 0.0f;
 #pragma unroll
-            for (int k = 0; k < kConvMaxTaps - 1; ++k) if (k == taps - 1 + index) value = old[k];
+            for (int k = 0; k < MAXT - 1; ++k) if (k == taps - 1 + index) value = old[k];
           }
           sum = fmaf(w[j], value, sum);
           if (j == taps - 1) current = value;
@@ -101,7 +102,7 @@ __global__ void __launch_bounds__(kConvThreads) causal_conv_kernel(const ConvPar
     }
     if (state) {
 #pragma unroll
-      for (int k = 0; k < kConvMaxTaps - 1; ++k) {
+      for (int k = 0; k < MAXT - 1; ++k) {
         if (k < taps - 1) {
           const int index = count - (taps - 1) + k;
           float value;
@@ -109,7 +110,7 @@ __global__ void __launch_bounds__(kConvThreads) causal_conv_kernel(const ConvPar
           else {
             value = 0.0f;
 #pragma unroll
-            for (int m = 0; m < kConvMaxTaps - 1; ++m) if (m == taps - 1 + index) value = old[m];
+            for (int m = 0; m < MAXT - 1; ++m) if (m == taps - 1 + index) value = old[m];
           }
           state[static_cast<size_t>(k) * p.channels + c] = value;
         }
@@ -126,7 +127,7 @@ __global__ void __launch_bounds__(kConvThreads) causal_conv_kernel(const ConvPar
     if (index < taps - 1) continue;
     float sum = 0.0f, current = 0.0f;
 #pragma unroll
-    for (int j = 0; j < kConvMaxTaps; ++j) {
+    for (int j = 0; j < MAXT; ++j) {
       if (j < taps) {
         const float value = p.x[static_cast<size_t>(t - (taps - 1) + j) * p.x_stride + c];
         sum = fmaf(w[j], value, sum);
@@ -148,9 +149,15 @@ VIPERA_API int vipera_causal_conv(const ConvParams* params, int out_dtype, int s
   p.segments = (single && p.taps > 1) ? 0 : (p.num_tokens + kConvSegment - 1) / kConvSegment;
   dim3 grid((p.channels + kConvThreads - 1) / kConvThreads, p.num_entries + p.segments);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (out_dtype == VIPERA_BF16) return vipera_launch(causal_conv_kernel<__nv_bfloat16>, grid, kConvThreads, 0, s, p);
-  if (out_dtype == VIPERA_F32) return vipera_launch(causal_conv_kernel<float>, grid, kConvThreads, 0, s, p);
-  return VIPERA_BAD_DTYPE;
+  if (out_dtype != VIPERA_BF16 && out_dtype != VIPERA_F32) return VIPERA_BAD_DTYPE;
+#define CONV_CASE(N)                                                                                          \
+  if (p.taps <= N) {                                                                                          \
+    if (out_dtype == VIPERA_BF16) return vipera_launch(causal_conv_kernel<__nv_bfloat16, N>, grid, kConvThreads, 0, s, p); \
+    return vipera_launch(causal_conv_kernel<float, N>, grid, kConvThreads, 0, s, p);                          \
+  }
+  CONV_CASE(4) CONV_CASE(8) CONV_CASE(kConvMaxTaps)
+#undef CONV_CASE
+  return VIPERA_BAD_SHAPE;
 }
 
 VIPERA_API int vipera_causal_conv_params_size() { return static_cast<int>(sizeof(ConvParams)); }
