@@ -68,12 +68,18 @@ ODD = config([attention_layer(heads=1, kv_heads=1, dim=18, scale=0.7, size=1000,
               mamba_layer(inner=24, state=37, dt_rank=9, conv=5, ff=16)],
              width=100, vocab=97, eps=1e-4, taps=1, scale=1.0)
 LONG_TAPS = config([mamba_layer(inner=48, state=8, dt_rank=4, conv=7, ff=32), parallel_layer()], width=64, taps=11)
+# Products with very few rows against inner sizes the tensor-core products take: a step-size rank and a
+# decay rank of one, three states, single heads of eight values.
+NARROW = config([mamba_layer(inner=64, state=3, dt_rank=1, conv=2, ff=16),
+                 parallel_layer(heads=1, kv_heads=1, dim=8, vdim=8, scale=0.6, r_heads=1, r_dim=8, r_vdim=8, tau=3.0, rank=1),
+                 attention_layer(heads=1, kv_heads=1, dim=8, scale=0.5, size=5, rot_dims=4, scaling=False)],
+                width=64, vocab=50, taps=2)
 ONLY_ATTENTION = config([attention_layer()])
 ONLY_MAMBA = config([mamba_layer()])
 ONLY_PARALLEL = config([parallel_layer()])
 ONLY_FF = config([attention_layer(ff=56)])
 
-CONFIGS = {"mixed": MIXED, "wide": WIDE, "odd": ODD, "long_taps": LONG_TAPS, "attention": ONLY_ATTENTION,
+CONFIGS = {"mixed": MIXED, "wide": WIDE, "odd": ODD, "long_taps": LONG_TAPS, "narrow": NARROW, "attention": ONLY_ATTENTION,
            "mamba": ONLY_MAMBA, "parallel": ONLY_PARALLEL, "ff": ONLY_FF}
 
 # How stored tensors are changed (by the end of their names): ("mul", x) or ("add", x).

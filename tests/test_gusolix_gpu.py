@@ -217,7 +217,7 @@ def test_far_tokens_reach_through_the_states():
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["odd", "long_taps"])
+@pytest.mark.parametrize("name", ["odd", "long_taps", "narrow"])
 def test_other_sizes(name, dtype):
     """Sizes and options the other configurations lack (see gusolix_cases): whole, in portions with
     a second request beside it, and decoding."""
