@@ -91,9 +91,10 @@ constexpr int kGlaWarps = 8;      // value tiles (of 32 columns) a block covers
 // scaled queries of kGlaTile tokens at a time are staged in shared memory by the whole block (they
 // are the same for every column); a token then costs a warp one coalesced load of v, broadcast
 // reads of the staged rows, and 2 * ROWS multiply-adds.
-template <int ROWS>
+// ENDS: the pass that only finds the chunks' end states (mode 1): no queries, no outputs.
+template <int ROWS, bool ENDS>
 __global__ void __launch_bounds__(kGlaWarps * 32) gla_scan_kernel(const GlaParams p) {
-  __shared__ __align__(16) float staged[3][kGlaTile][ROWS];   // decays, keys, queries
+  __shared__ __align__(16) float staged[ENDS ? 2 : 3][kGlaTile][ROWS];   // decays, keys, queries
   pdl_launch_dependents();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int share = blockIdx.x % p.shares, tiles0 = (blockIdx.x / p.shares) * kGlaWarps;
@@ -137,7 +138,7 @@ __global__ void __launch_bounds__(kGlaWarps * 32) gla_scan_kernel(const GlaParam
       const float* row = p.proj + static_cast<size_t>(t0 + tt) * p.proj_width + head * p.dim + row0 + r;
       staged[0][tt][r] = valid ? p.z[(static_cast<size_t>(t0 + tt) * p.heads + head) * p.dim + row0 + r] : 0.0f;
       staged[1][tt][r] = valid ? row[p.k_off] : 0.0f;
-      staged[2][tt][r] = valid ? row[p.q_off] * p.q_scale : 0.0f;
+      if (!ENDS) staged[2][tt][r] = valid ? row[p.q_off] * p.q_scale : 0.0f;
     }
     __syncthreads();
     float v_next = v_column[static_cast<size_t>(t0) * p.proj_width];
@@ -149,17 +150,19 @@ __global__ void __launch_bounds__(kGlaWarps * 32) gla_scan_kernel(const GlaParam
       for (int r = 0; r < ROWS; r += 4) {
         const float4 alpha = *reinterpret_cast<const float4*>(&staged[0][tt][r]);
         const float4 k = *reinterpret_cast<const float4*>(&staged[1][tt][r]);
-        const float4 q = *reinterpret_cast<const float4*>(&staged[2][tt][r]);
         s[r] = fmaf(alpha.x, s[r], k.x * v);
-        o = fmaf(s[r], q.x, o);
         s[r + 1] = fmaf(alpha.y, s[r + 1], k.y * v);
-        o = fmaf(s[r + 1], q.y, o);
         s[r + 2] = fmaf(alpha.z, s[r + 2], k.z * v);
-        o = fmaf(s[r + 2], q.z, o);
         s[r + 3] = fmaf(alpha.w, s[r + 3], k.w * v);
-        o = fmaf(s[r + 3], q.w, o);
+        if (!ENDS) {
+          const float4 q = *reinterpret_cast<const float4*>(&staged[ENDS ? 0 : 2][tt][r]);
+          o = fmaf(s[r], q.x, o);
+          o = fmaf(s[r + 1], q.y, o);
+          o = fmaf(s[r + 2], q.z, o);
+          o = fmaf(s[r + 3], q.w, o);
+        }
       }
-      if (live && p.mode != 1) partial[static_cast<size_t>(t0 + tt) * out_width + column] = o;
+      if (!ENDS && live) partial[static_cast<size_t>(t0 + tt) * out_width + column] = o;
     }
   }
   if (live && p.mode != 3) {
@@ -249,9 +252,14 @@ VIPERA_API int vipera_gla(const GlaParams* params, int out_dtype, void* stream) 
     const int tiles = (p.vdim + 31) / 32;
     const int warps = std::min(tiles, kGlaWarps);
     dim3 grid(p.shares * ((tiles + kGlaWarps - 1) / kGlaWarps), p.heads, mode == 0 ? p.num_entries : p.num_jobs);
-    if (rows == 8) return vipera_launch(gla_scan_kernel<8>, grid, warps * 32, 0, s, p);
-    if (rows == 16) return vipera_launch(gla_scan_kernel<16>, grid, warps * 32, 0, s, p);
-    return vipera_launch(gla_scan_kernel<32>, grid, warps * 32, 0, s, p);
+    if (mode == 1) {
+      if (rows == 8) return vipera_launch(gla_scan_kernel<8, true>, grid, warps * 32, 0, s, p);
+      if (rows == 16) return vipera_launch(gla_scan_kernel<16, true>, grid, warps * 32, 0, s, p);
+      return vipera_launch(gla_scan_kernel<32, true>, grid, warps * 32, 0, s, p);
+    }
+    if (rows == 8) return vipera_launch(gla_scan_kernel<8, false>, grid, warps * 32, 0, s, p);
+    if (rows == 16) return vipera_launch(gla_scan_kernel<16, false>, grid, warps * 32, 0, s, p);
+    return vipera_launch(gla_scan_kernel<32, false>, grid, warps * 32, 0, s, p);
   };
   const size_t decays = static_cast<size_t>(p.num_tokens) * p.heads * p.dim;
   int status = vipera_launch(gla_decay_kernel, dim3(static_cast<unsigned>(std::min<size_t>((decays + 255) / 256, 4096))), 256, 0, s, p);

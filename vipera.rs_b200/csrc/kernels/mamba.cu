@@ -78,7 +78,8 @@ __device__ __forceinline__ float scan_exp(float v) { return expf(v); }
 template <>
 __device__ __forceinline__ float scan_exp<__nv_bfloat16>(float v) { return __expf(v); }
 
-template <typename TO, int NPL>
+// ENDS: the pass that only finds the chunks' end states (mode 1): no C rows, no gate, no outputs.
+template <typename TO, int NPL, bool ENDS>
 __global__ void __launch_bounds__(kScanThreads) mamba_scan_kernel(const ScanParams p, int tile) {
   extern __shared__ __align__(16) float staged[];
   pdl_launch_dependents();
@@ -138,7 +139,7 @@ __global__ void __launch_bounds__(kScanThreads) mamba_scan_kernel(const ScanPara
       const float pre = valid ? p.dt_pre[at] : 0.0f;
       dt_s[index] = pre > 20.0f ? pre : log1pf(expf(pre));
       x_s[index] = valid ? p.x[at] : 0.0f;
-      z_s[index] = (valid && p.mode != 1) ? p.z[static_cast<size_t>(t0 + tt) * p.z_stride + p.z_offset + c0 + cl] : 0.0f;
+      if (!ENDS) z_s[index] = valid ? p.z[static_cast<size_t>(t0 + tt) * p.z_stride + p.z_offset + c0 + cl] : 0.0f;
     }
     for (int index = threadIdx.x; index < count * width; index += kScanThreads)
       bc_s[index] = p.bc[static_cast<size_t>(t0) * width + index];
@@ -155,15 +156,17 @@ __global__ void __launch_bounds__(kScanThreads) mamba_scan_kernel(const ScanPara
         // four states a lane, rows of B and C that start on 16 bytes: one read each
         if (sub * 4 < p.states) {
           const float4 b4 = *reinterpret_cast<const float4*>(b_row + sub * 4);
-          const float4 c4 = *reinterpret_cast<const float4*>(c_row + sub * 4);
           s[0] = fmaf(scan_exp<TO>(dt * a[0]), s[0], dtx * b4.x);
-          y = fmaf(s[0], c4.x, y);
           s[1 % NPL] = fmaf(scan_exp<TO>(dt * a[1 % NPL]), s[1 % NPL], dtx * b4.y);
-          y = fmaf(s[1 % NPL], c4.y, y);
           s[2 % NPL] = fmaf(scan_exp<TO>(dt * a[2 % NPL]), s[2 % NPL], dtx * b4.z);
-          y = fmaf(s[2 % NPL], c4.z, y);
           s[3 % NPL] = fmaf(scan_exp<TO>(dt * a[3 % NPL]), s[3 % NPL], dtx * b4.w);
-          y = fmaf(s[3 % NPL], c4.w, y);
+          if (!ENDS) {
+            const float4 c4 = *reinterpret_cast<const float4*>(c_row + sub * 4);
+            y = fmaf(s[0], c4.x, y);
+            y = fmaf(s[1 % NPL], c4.y, y);
+            y = fmaf(s[2 % NPL], c4.z, y);
+            y = fmaf(s[3 % NPL], c4.w, y);
+          }
         }
       } else {
 #pragma unroll
@@ -171,16 +174,17 @@ __global__ void __launch_bounds__(kScanThreads) mamba_scan_kernel(const ScanPara
           const int n = sub * NPL + j;
           if (n < p.states) {
             s[j] = fmaf(scan_exp<TO>(dt * a[j]), s[j], dtx * b_row[n]);
-            y = fmaf(s[j], c_row[n], y);
+            if (!ENDS) y = fmaf(s[j], c_row[n], y);
           }
         }
       }
-      if (p.mode == 1) continue;   // the pass that only finds the chunks' end states
-      for (int offset = lanes >> 1; offset > 0; offset >>= 1) y += __shfl_xor_sync(0xffffffffu, y, offset);
-      if (live && sub == 0) {
-        const float gate = z_s[tt * per_block + local];
-        y = fmaf(skip, x, y);
-        out[static_cast<size_t>(t0 + tt) * p.channels + c] = from_float<TO>(y * (gate / (1.0f + scan_exp<TO>(-gate))));
+      if (!ENDS) {
+        for (int offset = lanes >> 1; offset > 0; offset >>= 1) y += __shfl_xor_sync(0xffffffffu, y, offset);
+        if (live && sub == 0) {
+          const float gate = z_s[tt * per_block + local];
+          y = fmaf(skip, x, y);
+          out[static_cast<size_t>(t0 + tt) * p.channels + c] = from_float<TO>(y * (gate / (1.0f + scan_exp<TO>(-gate))));
+        }
       }
     }
   }
@@ -255,9 +259,14 @@ VIPERA_API int vipera_mamba_scan(const ScanParams* params, int out_dtype, void* 
     dim3 grid((p.channels + channels_per_block - 1) / channels_per_block, mode == 0 ? p.num_entries : p.num_jobs);
 #define SCAN_CASE(N)                                                                                     \
   if (per_lane == N) {                                                                                   \
+    if (mode == 1) {                                                                                     \
+      if (out_dtype == VIPERA_BF16)                                                                      \
+        return vipera_launch(mamba_scan_kernel<__nv_bfloat16, N, true>, grid, kScanThreads, shared_bytes, s, p, tile); \
+      return vipera_launch(mamba_scan_kernel<float, N, true>, grid, kScanThreads, shared_bytes, s, p, tile); \
+    }                                                                                                    \
     if (out_dtype == VIPERA_BF16)                                                                        \
-      return vipera_launch(mamba_scan_kernel<__nv_bfloat16, N>, grid, kScanThreads, shared_bytes, s, p, tile); \
-    return vipera_launch(mamba_scan_kernel<float, N>, grid, kScanThreads, shared_bytes, s, p, tile);       \
+      return vipera_launch(mamba_scan_kernel<__nv_bfloat16, N, false>, grid, kScanThreads, shared_bytes, s, p, tile); \
+    return vipera_launch(mamba_scan_kernel<float, N, false>, grid, kScanThreads, shared_bytes, s, p, tile); \
   }
     SCAN_CASE(1) SCAN_CASE(2) SCAN_CASE(4) SCAN_CASE(8) SCAN_CASE(16)
 #undef SCAN_CASE
