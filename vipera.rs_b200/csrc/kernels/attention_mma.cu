@@ -169,6 +169,15 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
     if (row >= tokens_here) continue;
     if (sink) sum += exp2f(-row_max[r]);   // the sink's score is 0; the maximum is in units of log2
     const float inverse = 1.0f / sum;
+    if (VIRT) {   // the pairs' rows stay 32-bit: they are mixed in 32-bit afterwards
+      float* wide = reinterpret_cast<float*>(out) + (static_cast<size_t>(token0 + row) * out_heads + head) * D;
+#pragma unroll
+      for (int n = 0; n < D / 8; ++n) {
+        const int col = n * 8 + 2 * (lane & 3);
+        *reinterpret_cast<float2*>(wide + col) = make_float2(acc[n][2 * r] * inverse, acc[n][2 * r + 1] * inverse);
+      }
+      continue;
+    }
     __nv_bfloat16* dst = out + (static_cast<size_t>(token0 + row) * out_heads + head) * D;
 #pragma unroll
     for (int n = 0; n < D / 8; ++n) {
@@ -365,7 +374,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 }
 
 // grid: (tokens, heads); one block of D threads combines the splits of one row.
-template <int D, bool KEPT = false>
+// WIDE: the output is 32-bit (behind the VIRT instance, whose rows are mixed in 32-bit afterwards).
+template <int D, bool KEPT = false, bool WIDE = false>
 __global__ void attention_combine_kernel(const float* __restrict__ partial_ml, const float* __restrict__ partial_out,
                                          int slices, __nv_bfloat16* __restrict__ out, int num_heads,
                                          const int* __restrict__ positions, int window, int chunk,
@@ -436,7 +446,8 @@ __global__ void attention_combine_kernel(const float* __restrict__ partial_ml, c
     }
   }
   if (KEPT && sink) total += exp2f(-mine);   // the maxima are in units of log2
-  out[out_row * D + threadIdx.x] = __float2bfloat16_rn(value / total);
+  if (WIDE) reinterpret_cast<float*>(out)[out_row * D + threadIdx.x] = value / total;
+  else out[out_row * D + threadIdx.x] = __float2bfloat16_rn(value / total);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -848,7 +859,7 @@ int launch_decode_pairs(const void* q, void* out, const void* k_pool, const void
       num_heads, num_kv_heads, scale, 0, chunk, num_splits, partial_ml, partial_out, static_cast<const int*>(nullptr), 0,
       num_kv_heads);
   if (status != VIPERA_OK) return status;
-  return vipera_launch(attention_combine_kernel<D>, dim3(num_entries, pairs), D, 0, s,
+  return vipera_launch(attention_combine_kernel<D, false, true>, dim3(num_entries, pairs), D, 0, s,
       static_cast<const float*>(partial_ml), static_cast<const float*>(partial_out), num_splits,
       static_cast<__nv_bfloat16*>(out), pairs, positions, 0, chunk, static_cast<const int*>(nullptr), 0, 0);
 }
@@ -878,7 +889,7 @@ static int run_prefill(const void* q, void* out, const void* k_pool, const void*
 }
 
 // Causal attention of every query head against the values of every KV head (keys: the query head's
-// own KV head): out [tokens, heads * kv_heads, d], row g * kv_heads + c = softmax(q_g k^T) v_c.
+// own KV head): out, 32-bit, [tokens, heads * kv_heads, d], row g * kv_heads + c = softmax(q_g k^T) v_c.
 VIPERA_API int vipera_attention_prefill_pairs(const void* q, void* out, const void* k_pool, const void* v_pool,
                                               const int* entry_starts, const int* entry_pos0, const int* block_table,
                                               int table_width, int page_size, int num_entries, int num_tokens,
@@ -957,7 +968,7 @@ static int run_decode(const void* q, void* out, const void* k_pool, const void* 
 }
 
 // A step of single tokens, every query head against every KV head's values (see
-// vipera_attention_prefill_pairs): out [entries, heads * kv_heads, d]; the scratch is sized for
+// vipera_attention_prefill_pairs): out, 32-bit, [entries, heads * kv_heads, d]; the scratch is sized for
 // heads * kv_heads heads.
 VIPERA_API int vipera_attention_decode_pairs(const void* q, void* out, const void* k_pool, const void* v_pool,
                                              const int* positions, const int* block_table, int table_width,

@@ -294,29 +294,29 @@ static int launch_talk(int hpw, dim3 grid, size_t shared_bytes, cudaStream_t s, 
 
 // q [tokens, heads, d], out [tokens, heads, value_dim], mix [heads, heads] 32-bit (row h holds the
 // weights of head h's mix); pools and tables as in the general attention kernel.
-// The mix applied to attention outputs of every (query head, KV head) pair: with a [tokens, heads *
+// The mix applied to the 32-bit attention outputs of every (query head, KV head) pair: with a [tokens, heads *
 // kv_heads, dv] = softmax(q_g k^T) v_c at row g * kv_heads + c, out[t, h] = out_scale * sum_g mix[h, g]
 // a[t, g * kv_heads + kv(h)] (the same sum as mixing the weights, the values being shared).  32-bit sums.
 template <typename T>
 __global__ void __launch_bounds__(256)
-talk_combine_kernel(const T* __restrict__ pairs, const float* __restrict__ mix, T* __restrict__ out, int num_heads,
+talk_combine_kernel(const float* __restrict__ pairs, const float* __restrict__ mix, T* __restrict__ out, int num_heads,
                     int num_kv_heads, int value_dim, float out_scale) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
   const int group = num_heads / num_kv_heads;
-  const T* row = pairs + static_cast<size_t>(t) * num_heads * num_kv_heads * value_dim;
+  const float* row = pairs + static_cast<size_t>(t) * num_heads * num_kv_heads * value_dim;
   for (int item = threadIdx.x; item < num_heads * value_dim; item += blockDim.x) {
     const int h = item / value_dim, e = item % value_dim;
     const int kv = h / group;
     float sum = 0.0f;
     for (int g = 0; g < num_heads; ++g)
-      sum = fmaf(mix[h * num_heads + g], to_float<T>(row[(static_cast<size_t>(g) * num_kv_heads + kv) * value_dim + e]), sum);
+      sum = fmaf(mix[h * num_heads + g], row[(static_cast<size_t>(g) * num_kv_heads + kv) * value_dim + e], sum);
     out[static_cast<size_t>(t) * num_heads * value_dim + item] = from_float<T>(sum * out_scale);
   }
 }
 
-VIPERA_API int vipera_talk_combine(const void* pairs, const float* mix, void* out, int dtype, int num_tokens,
+VIPERA_API int vipera_talk_combine(const float* pairs, const float* mix, void* out, int dtype, int num_tokens,
                                    int num_heads, int num_kv_heads, int value_dim, float out_scale, void* stream) {
   if (num_tokens <= 0) return VIPERA_OK;
   if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads || value_dim <= 0) return VIPERA_BAD_SHAPE;
@@ -324,11 +324,10 @@ VIPERA_API int vipera_talk_combine(const void* pairs, const float* mix, void* ou
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dtype == VIPERA_BF16)
     return vipera_launch(talk_combine_kernel<__nv_bfloat16>, dim3(num_tokens), 256, 0, s,
-                         static_cast<const __nv_bfloat16*>(pairs), mix, static_cast<__nv_bfloat16*>(out), num_heads,
-                         num_kv_heads, value_dim, out_scale);
+                         pairs, mix, static_cast<__nv_bfloat16*>(out), num_heads, num_kv_heads, value_dim, out_scale);
   if (dtype == VIPERA_F32)
-    return vipera_launch(talk_combine_kernel<float>, dim3(num_tokens), 256, 0, s, static_cast<const float*>(pairs), mix,
-                         static_cast<float*>(out), num_heads, num_kv_heads, value_dim, out_scale);
+    return vipera_launch(talk_combine_kernel<float>, dim3(num_tokens), 256, 0, s, pairs, mix, static_cast<float*>(out),
+                         num_heads, num_kv_heads, value_dim, out_scale);
   return VIPERA_BAD_DTYPE;
 }
 

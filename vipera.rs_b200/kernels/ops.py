@@ -1198,7 +1198,7 @@ def attention_talk_prefill(q: torch.Tensor, out: torch.Tensor, pairs: torch.Tens
                            scale: float, out_scale: float = 1.0) -> None:
     """The same result as ``attention_talk`` for steps with portions, on the tensor cores (bfloat16,
     head sizes 64 and 128, values as long as keys): the flash kernel computes softmax(q_g k^T) v_c
-    for every pair of a query head g and a KV head c into ``pairs`` [tokens, heads * kv_heads * d],
+    for every pair of a query head g and a KV head c into the float32 ``pairs`` [tokens, heads * kv_heads * d],
     and a second kernel forms ``out[t, h] = out_scale * sum_g mix[h, g] pairs[t, g, kv(h)]`` in 32-bit
     (mixing the heads' weights is linear in them, and the values are shared)."""
     if head_dim not in MMA_HEAD_DIMS:
@@ -1212,7 +1212,7 @@ def attention_talk_prefill(q: torch.Tensor, out: torch.Tensor, pairs: torch.Tens
     if tuple(mix.shape) != (num_heads, num_heads):
         raise InvalidArgumentError("attention_talk_prefill: the mixing matrix must be [heads, heads]")
     fn = _function("attention_mma", "vipera_attention_prefill_pairs", [_c_void] * 7 + [_c_int] * 7 + [_c_float, _c_void])
-    _check(fn(_gpu(q, "q", torch.bfloat16), _gpu(pairs, "pairs", torch.bfloat16), _gpu(k_pool, "k_pool", torch.bfloat16),
+    _check(fn(_gpu(q, "q", torch.bfloat16), _gpu(pairs, "pairs", torch.float32), _gpu(k_pool, "k_pool", torch.bfloat16),
               _gpu(v_pool, "v_pool", torch.bfloat16), _gpu(entry_starts, "entry_starts", torch.int32),
               _gpu(entry_pos0, "entry_pos0", torch.int32), _gpu(block_table, "block_table", torch.int32),
               block_table.shape[1], k_pool.shape[1], int(num_entries), count, num_heads, num_kv_heads, head_dim,
@@ -1228,7 +1228,7 @@ def attention_talk_decode(q: torch.Tensor, out: torch.Tensor, pairs: torch.Tenso
                           num_heads: int, num_kv_heads: int, head_dim: int, scale: float, chunk: int, num_splits: int,
                           scratch: torch.Tensor, out_scale: float = 1.0) -> None:
     """``attention_talk_prefill`` for a step of single tokens: the split-key kernel computes every
-    (query head, KV head) pair into ``pairs`` [entries, heads * kv_heads * d] (``chunk``, ``num_splits``
+    (query head, KV head) pair into the float32 ``pairs`` [entries, heads * kv_heads * d] (``chunk``, ``num_splits``
     and ``scratch`` as for ``attention_decode``, the scratch sized for heads * kv_heads heads), then
     the mix of the pairs' outputs."""
     if head_dim not in MMA_HEAD_DIMS:
@@ -1241,7 +1241,7 @@ def attention_talk_decode(q: torch.Tensor, out: torch.Tensor, pairs: torch.Tenso
         raise InvalidArgumentError("attention_talk_decode: cache pools must be [pages, page_size, kv_heads, d]")
     fn = _function("attention_mma", "vipera_attention_decode_pairs",
                    [_c_void] * 6 + [_c_int] * 6 + [_c_float, _c_int, _c_int, _c_void, ctypes.c_size_t, _c_void])
-    _check(fn(_gpu(q, "q", torch.bfloat16), _gpu(pairs, "pairs", torch.bfloat16), _gpu(k_pool, "k_pool", torch.bfloat16),
+    _check(fn(_gpu(q, "q", torch.bfloat16), _gpu(pairs, "pairs", torch.float32), _gpu(k_pool, "k_pool", torch.bfloat16),
               _gpu(v_pool, "v_pool", torch.bfloat16), _gpu(positions, "positions", torch.int32),
               _gpu(block_table, "block_table", torch.int32), block_table.shape[1], k_pool.shape[1], count, num_heads,
               num_kv_heads, head_dim, float(scale), int(chunk), int(num_splits), _gpu(scratch, "scratch", torch.float32),

@@ -254,7 +254,7 @@ class GQAttention(Mixer):
                 scratch = ctx.workspace.get(
                     "attention.partials",
                     (ops.attention_decode_scratch_floats(ctx.num_entries, heads * kv_heads, d, splits),), torch.float32)
-                pairs = ctx.workspace.get("attention.talk_pairs", (count, heads * kv_heads * d), ctx.dtype)
+                pairs = ctx.workspace.get("attention.talk_pairs", (count, heads * kv_heads * d), torch.float32)
                 ops.attention_talk_decode(q, mixed, pairs, cache.k, cache.v, self.talk, positions=ctx.positions,
                                           block_table=table, num_heads=heads, num_kv_heads=kv_heads, head_dim=d,
                                           scale=self.scale, chunk=chunk, num_splits=splits, scratch=scratch,
@@ -263,7 +263,7 @@ class GQAttention(Mixer):
             if not ctx.all_single and tensor_cores and count >= self.TALK_PAIRS_FROM:
                 # steps with portions on the tensor cores: every (query head, KV head) pair through the
                 # flash kernel, then the mix of the pairs' outputs
-                pairs = ctx.workspace.get("attention.talk_pairs", (count, heads * kv_heads * d), ctx.dtype)
+                pairs = ctx.workspace.get("attention.talk_pairs", (count, heads * kv_heads * d), torch.float32)
                 ops.attention_talk_prefill(q, mixed, pairs, cache.k, cache.v, self.talk, entry_starts=ctx.entry_starts,
                                            entry_pos0=ctx.entry_pos0, block_table=table, num_entries=ctx.num_entries,
                                            num_heads=heads, num_kv_heads=kv_heads, head_dim=d, scale=self.scale,
